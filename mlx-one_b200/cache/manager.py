@@ -4,10 +4,11 @@ Cache entries (one per layer call that keeps something) with equal needs form a 
 A paged group owns one pool of pages; a request has one block table per paged group and
 all entries of the group use the same page numbers, each in its own storage. Groups with
 a window give a page back as soon as every position in it has left the window of the next
-query. A fixed-state group owns a pool of slots; a request has one slot per group.
+query, and groups whose queries read only their own chunk of positions give back the pages of
+chunks that have ended. A fixed-state group owns a pool of slots; a request has one slot per group.
 
 Storage (on the device, in place):
-  paged group   [entries, 2, pages, kv_heads, page_size, head_dim]
+  paged group   [entries, planes, pages, kv_heads, page_size, head_dim]
   state group   [entries, slots, *shape]
 
 Requests are opened, grown before a step (``grow``), advanced after it (``advance``) and
@@ -104,7 +105,7 @@ class CacheManager:
                 storage = None
                 if allocate:
                     # one page beyond the pool's: the scratch page (see ``scratch_page``)
-                    storage = torch.zeros((len(entries), 2, pages + 1, need.kv_heads, page_size,
+                    storage = torch.zeros((len(entries), need.planes, pages + 1, need.kv_heads, page_size,
                                            need.head_dim), dtype=dtype, device=self.device)
                 group = len(self.paged)
                 self.paged.append(PagedGroup(need, tuple(entries), IndexPool(pages, "page"),
@@ -114,7 +115,7 @@ class CacheManager:
             elif isinstance(need, FixedState):
                 storage = None
                 if allocate:
-                    kind = torch.float32 if need.dtype == "float32" else dtype
+                    kind = {"float32": torch.float32, "int32": torch.int32}.get(need.dtype, dtype)
                     # one slot beyond the pool's: the scratch slot
                     storage = torch.zeros((len(entries), max_requests + 1, *need.shape),
                                           dtype=kind, device=self.device)
@@ -139,11 +140,14 @@ class CacheManager:
     def pages_for(self, group: PagedGroup, tokens: int) -> int:
         """Most pages a request of ``tokens`` tokens holds in ``group`` at any time."""
         whole = ceil_div(tokens, self.page_size)
-        if group.need.window is None:
+        # (a chunk's first query still reads nothing before it, its last one chunk - 1 keys)
+        reach = min((span for span in (group.need.window, group.need.chunk) if span is not None),
+                    default=None)
+        if reach is None:
             return whole
-        # keys of the last window-1 positions, the step's own tokens, and one ragged edge
+        # keys of the last reach-1 positions, the step's own tokens, and one ragged edge
         step = min(self.max_step_tokens, tokens)
-        return min(whole, ceil_div(group.need.window - 1 + step, self.page_size) + 1)
+        return min(whole, ceil_div(reach - 1 + step, self.page_size) + 1)
 
     def fits_ever(self, tokens: int) -> bool:
         return all(self.pages_for(g, tokens) <= g.pool.count for g in self.paged)
@@ -227,11 +231,16 @@ class CacheManager:
         cache = self.get(request_id)
         cache.length += new_tokens
         for index, group in enumerate(self.paged):
-            window = group.need.window
-            if window is None:
+            window, chunk = group.need.window, group.need.chunk
+            if window is None and chunk is None:
                 continue
-            # the next query sits at position >= length and reads keys > query - window
-            first_needed = cache.length - window + 1
+            first_needed = 0
+            if window is not None:
+                # the next query sits at position >= length and reads keys > query - window
+                first_needed = cache.length - window + 1
+            if chunk is not None:
+                # ... and nothing before the chunk that position ``length`` lies in
+                first_needed = max(first_needed, cache.length - cache.length % chunk)
             table = cache.tables[index]
             for block in range(min(max(first_needed, 0) // self.page_size, len(table))):
                 if table[block] >= 0:

@@ -31,6 +31,7 @@ _BUILTIN = {
     "lfm2": "mlx_one_b200.architectures.lfm2:ARCHITECTURE",
     "galarax": "mlx_one_b200.architectures.galarax:ARCHITECTURE",
     "farorax": "mlx_one_b200.architectures.farorax:ARCHITECTURE",
+    "lamisun": "mlx_one_b200.architectures.lamisun:ARCHITECTURE",
 }
 _REGISTERED: dict[str, Architecture] = {}
 

@@ -41,7 +41,7 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ kv,
     for (int e = lane; e < head_dim; e += 32) query[e] = to_float<T>(q_row[e]) * scale;
     __syncwarp();
 
-    const int lowest = window > 0 ? max(position - window + 1, 0) : 0;
+    const int lowest = first_visible_key(position, window);
     // A sink is a term exp(sink) of the denominator that has no key and no value: the softmax
     // starts from it (maximum = sink, sum = 1, output = 0) instead of from nothing.
     float running_max = -INFINITY, running_sum = 0.f;

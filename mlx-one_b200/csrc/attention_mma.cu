@@ -297,7 +297,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
     }
     const int first_position = before + row_start;
     const int last_position = first_position + rows - 1;
-    const int lowest = window > 0 ? max(first_position - window + 1, 0) : 0;
+    const int lowest = first_visible_key(first_position, window);
     const int tile_first = lowest / KEYS, tile_last = last_position / KEYS;
 
     load_tile<HD, KEYS>(k_tiles, v_tiles, pages, tile_first * KEYS, lowest, last_position, threadIdx.x,
@@ -311,7 +311,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
         const int row = warp * 16 + (lane >> 2) + i * 8;
         const int position = first_position + row;
         limit_hi[i] = row < rows ? position : -1;
-        limit_lo[i] = window > 0 ? max(position - window + 1, 0) : 0;
+        limit_lo[i] = first_visible_key(position, window);
     }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     if (sinks != nullptr) {
@@ -331,7 +331,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
     // row's position (rows beyond the portion's end see nothing, so such a warp always masks)
     const int warp_first = first_position + warp * 16;
     const bool warp_whole = warp * 16 + 15 < rows;
-    const int open_lo = window > 0 ? max(warp_first + 15 - window + 1, 0) : 0;
+    const int open_lo = first_visible_key(warp_first + 15, window);
 
     for (int tile = tile_first; tile <= tile_last; ++tile) {
         const int buffer = (tile - tile_first) & 1;
@@ -450,7 +450,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
     const int g = lane >> 2, t = lane & 3;
 
     const int position = positions[request];
-    const int lowest = window > 0 ? max(position - window + 1, 0) : 0;
+    const int lowest = first_visible_key(position, window);
     const int tile_first = lowest / KEYS, tile_count = position / KEYS - tile_first + 1;
     const int per_split = (tile_count + splits - 1) / splits;
     const int my_first = tile_first + split * per_split;

@@ -313,7 +313,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                 item.tokens_here = min(tile_tokens, count - token_start);
                 item.first_position = history[r] + token_start;
                 const int last_position = item.first_position + item.tokens_here - 1;
-                const int lowest = window > 0 ? max(item.first_position - window + 1, 0) : 0;
+                const int lowest = first_visible_key(item.first_position, window);
                 item.tile_first = lowest / KEYS;
                 item.tile_count = last_position / KEYS - item.tile_first + 1;
                 if (splits > 1) {
@@ -399,7 +399,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
             ++taken;
             const int* table = block_table + (size_t)item.request * table_width;
             const int last_position = item.first_position + item.tokens_here - 1;
-            const int lowest = window > 0 ? max(item.first_position - window + 1, 0) : 0;
+            const int lowest = first_visible_key(item.first_position, window);
             // this lane's box of the item's tile j: its rows in the cache, if some query row
             // may see its keys
             auto box_row = [&](int j) {
@@ -536,11 +536,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
             const int position = item.first_position + token;
             const int last_position = item.first_position + item.tokens_here - 1;
             const int limit_hi = valid ? position : -1;
-            const int limit_lo = window > 0 ? max(position - window + 1, 0) : 0;
+            const int limit_lo = first_visible_key(position, window);
             // keys that every row of the block sees: from the last row's lower limit to the
             // first row's position; a block with rows beyond the portion's end always masks
             const bool whole = item.tokens_here == tile_tokens;
-            const int open_lo = window > 0 ? max(last_position - window + 1, 0) : 0;
+            const int open_lo = first_visible_key(last_position, window);
             // m: the maximum that the exponentials are taken against. It follows the running
             // maximum only when that has moved by more than LAZY (in powers of two), so that the
             // output so far, which the product warp accumulates in tensor memory over the item's

@@ -17,11 +17,16 @@ from .spec import PartSpec, TensorSpec
 class PagedKeyValues:
     """A mixer that keeps a key and a value vector per token and per key head. Layers
     whose need is equal share pages and a block table. ``window``: only the last
-    ``window`` positions are ever read again, so earlier pages may be given back."""
+    ``window`` positions are ever read again, so earlier pages may be given back. ``chunk``:
+    a query reads only keys of its own chunk of ``chunk`` positions (counted from 0), so the
+    pages of chunks that have ended may be given back. ``planes``: 2 for keys and values; 1 for
+    a mixer that keeps one row per token and reads it as key and as value."""
 
     kv_heads: int
     head_dim: int
     window: int | None = None
+    chunk: int | None = None
+    planes: int = 2
 
 
 @dataclass(frozen=True)
@@ -30,7 +35,7 @@ class FixedState:
     a slot. The slot is zero when a request gets it."""
 
     shape: tuple[int, ...]
-    dtype: str = "compute"          # "compute" = the engine's dtype, or "float32"
+    dtype: str = "compute"          # "compute" = the engine's dtype, "float32" or "int32"
 
 
 # ----------------------------------------------------------------------- run time
@@ -48,7 +53,7 @@ class Runtime:
 @dataclass
 class PagedView:
     """One cache entry of a paged group as a step sees it. ``kv`` is
-    [2, pages, kv_heads, page_size, head_dim]; ``block_table`` is int32 [requests, width]
+    [planes, pages, kv_heads, page_size, head_dim]; ``block_table`` is int32 [requests, width]
     with -1 where a page was given back."""
 
     kv: torch.Tensor
@@ -242,6 +247,19 @@ class PositionEncoding(Part):
         return 1.0
 
 
+class Embedding(Part):
+    """From a step's token ids to the 32-bit stream's first value."""
+
+    @classmethod
+    def cache_need(cls, spec: PartSpec):
+        """``FixedState`` or None: what the embedding keeps per request."""
+        return None
+
+    def forward(self, ctx: "StepContext", cache: Any, out: torch.Tensor | None = None):
+        """float32 [tokens, hidden] (written to ``out`` if given)."""
+        raise NotImplementedError
+
+
 class Block(Part):
     """Arranges a layer's parts. Gets the built parts by role."""
 
@@ -255,6 +273,18 @@ class Block(Part):
 
     # the factor with which the output that ``forward`` returns is still to be added
     pending_scale = 1.0
+    # True: ``forward`` is also given ``streams=(kept, place)``, the 32-bit streams of the step
+    # [calls + 2, tokens, hidden] and this call's number in the order. kept[0] is the embedding's
+    # output, kept[place + 1] is ``residual`` itself, which the block turns into its result in
+    # place; the block leaves what the next call reads in kept[place + 2] and returns
+    # (that stream, pending output) instead of the pending output alone.
+    keeps_streams = False
+
+    @classmethod
+    def cache_need(cls, spec: PartSpec):
+        """What the block itself keeps per request besides its mixer's cache: None, or a mapping
+        name -> need; ``forward`` is then given ``own_cache=`` (a mapping name -> view)."""
+        return None
 
     def forward(self, residual: torch.Tensor, delta: torch.Tensor | None, ctx: StepContext,
                 cache: Any, write: bool) -> torch.Tensor | None:

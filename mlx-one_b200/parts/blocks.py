@@ -2,8 +2,9 @@
 
 from __future__ import annotations
 
-from .base import Block
+from .base import Block, FixedState
 from .registry import BLOCKS
+from .spec import TensorSpec
 
 
 @BLOCKS.register("prenorm")
@@ -47,3 +48,75 @@ class PreNormBlock(Block):
         if self._fuses(self.feed_forward):
             return self.feed_forward.forward(normed, ctx, residual=residual)
         return self.feed_forward.forward(normed, ctx)
+
+
+@BLOCKS.register("outnorm")
+class OutputNormBlock(Block):
+    """x <- x + norm1(mixer(in1(x))); x <- x + norm2(feed_forward(in2(x))): the norms are applied
+    to the parts' outputs, the parts read the stream itself (rounded to the compute dtype).
+    A layer without a feed-forward ends after the mixer. Parameters:
+
+    ``taps`` (None: in(x) = x): in(x) = x + conv(x), a causal convolution over time on every
+    channel of the 32-bit stream, conv(x)_t = sum_j w[:, j] x_(t - taps + 1 + j) with nothing
+    before a sequence's start; ``conv1`` and ``conv2`` [hidden, taps] are the two sublayers'
+    weights. The last taps - 1 rows of x that each sublayer read are kept per request in 32-bit.
+
+    ``streams`` (None: the layer's result goes on as it is): the number n of streams that are
+    averaged after the layer, with the stored weights ``average`` [n]: what the next layer reads
+    is sum_j average[j] X_j, X_0 the embedding's output and X_(j+1) the result of the call j of
+    the order (before any averaging), so n is this call's number plus two."""
+
+    @classmethod
+    def tensors(cls, spec):
+        out = {}
+        if spec.get("taps"):
+            out["conv1"] = TensorSpec((spec["hidden"], spec["taps"]), "wide")
+            if spec.get("feed_forward", True):
+                out["conv2"] = TensorSpec((spec["hidden"], spec["taps"]), "wide")
+        if spec.get("streams"):
+            out["average"] = TensorSpec((spec["streams"],), "wide")
+        return out
+
+    @classmethod
+    def cache_need(cls, spec):
+        taps = spec.get("taps")
+        if not taps or taps < 2:
+            return None
+        sublayers = 2 if spec.get("feed_forward", True) else 1
+        return {"inputs": FixedState((sublayers, taps - 1, spec["hidden"]), "float32")}
+
+    def __init__(self, spec, tensors, runtime, **roles):
+        super().__init__(spec, tensors, runtime, **roles)
+        self.taps = spec.get("taps") or 0
+        self.conv1 = self.vector(tensors["conv1"]) if "conv1" in tensors else None
+        self.conv2 = self.vector(tensors["conv2"]) if "conv2" in tensors else None
+        self.average = self.vector(tensors["average"]) if "average" in tensors else None
+        self.keeps_streams = self.average is not None
+        for norm in (self.mixer_norm, self.feed_forward_norm):
+            if norm is not None and not hasattr(norm, "add_normed"):
+                raise ValueError("this block needs norms that can be applied to a part's output")
+
+    def _read(self, residual, kernel, ctx, own_cache, write, sublayer):
+        """What a sublayer reads: the stream (plus its convolution over time) in the compute dtype."""
+        view = (own_cache or {}).get("inputs")
+        return self.ops.stream_conv(residual, kernel, taps=self.taps, ctx=ctx, view=view,
+                                    sublayer=sublayer, write=write, dtype=self.runtime.dtype)
+
+    def forward(self, residual, delta, ctx, cache, write, own_cache=None, streams=None,
+                delta_scale=1.0):
+        if delta is not None:
+            raise ValueError("this block takes a stream with nothing pending")
+        mixed = self.mixer.forward(self._read(residual, self.conv1, ctx, own_cache, write, 0),
+                                   ctx, cache, write)
+        self.mixer_norm.add_normed(residual, mixed)
+        if self.feed_forward is not None:
+            out = self.feed_forward.forward(
+                self._read(residual, self.conv2, ctx, own_cache, write, 1), ctx)
+            self.feed_forward_norm.add_normed(residual, out)
+        if self.average is None:
+            return None
+        kept, place = streams
+        if self.average.numel() != place + 2:
+            raise ValueError(f"call {place} of the order averages {place + 2} streams, "
+                             f"{self.average.numel()} weights are stored")
+        return self.ops.stream_average(kept, self.average, place + 2, kept[place + 2]), None

@@ -52,16 +52,20 @@ class SwiGLU(FeedForward):
 class DenseFeedForward(FeedForward):
     """down(act(up x)), no gate, no biases. Parameters: ``hidden``, ``width``, ``activation``:
     ``relu2`` (the square of max(z, 0)), ``gelu_tanh`` (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715
-    z^3)))), ``silu`` or ``relu``. The activation is the up product's epilogue where the kernels
-    have one."""
+    z^3)))), ``silu``, ``relu``, or ``xielu``: with the two stored numbers ``act`` = (p, q), a =
+    softplus(p) and b = 1/2 + softplus(q), a z^2 + z / 2 above zero and b (e^z - 1 - z) + z / 2 at
+    and below it. The activation is the up product's epilogue where the kernels have one."""
 
-    ACTIVATIONS = ("relu2", "gelu_tanh", "silu", "relu")
+    ACTIVATIONS = ("relu2", "gelu_tanh", "silu", "relu", "xielu")
 
     @classmethod
     def tensors(cls, spec):
         hidden, width = spec["hidden"], spec["width"]
-        return {"up.weight": TensorSpec((width, hidden)),
-                "down.weight": TensorSpec((hidden, width))}
+        out = {"up.weight": TensorSpec((width, hidden)),
+               "down.weight": TensorSpec((hidden, width))}
+        if spec.get("activation") == "xielu":
+            out["act"] = TensorSpec((2,), "wide")
+        return out
 
     def __init__(self, spec, tensors, runtime):
         super().__init__(spec, tensors, runtime)
@@ -70,12 +74,18 @@ class DenseFeedForward(FeedForward):
             raise ValueError(f"unknown activation {self.activation!r}")
         self.up = self.matrix(tensors["up.weight"])
         self.down = self.matrix(tensors["down.weight"])
+        self.shape = {}
+        if self.activation == "xielu":
+            # the two factors, worked out once in 32-bit
+            p, q = tensors["act"].to(torch.float32).cpu()
+            softplus = torch.nn.functional.softplus
+            self.shape = dict(params=(float(softplus(p)), float(0.5 + softplus(q))))
 
     fuses_residual = True
     accepts_normed_input = True
 
     def forward(self, x, ctx, residual=None):
-        hidden = self.ops.linear_act(x, self.up, self.activation)
+        hidden = self.ops.linear_act(x, self.up, self.activation, **self.shape)
         if residual is None:
             return self.ops.linear(hidden, self.down)
         return self.ops.linear_add(hidden, self.down, None, residual)

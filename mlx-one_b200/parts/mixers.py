@@ -1,6 +1,7 @@
 """Sequence mixers: grouped-query attention over paged keys and values, the gated short
-convolution with a fixed-size state, the gated delta rule with a matrix state per head, and
-several mixers side by side on one input."""
+convolution with a fixed-size state, the gated delta rule with a matrix state per head,
+several mixers side by side on one input, attention over one latent row per token, and
+attention with two score maps per head."""
 
 from __future__ import annotations
 
@@ -436,3 +437,167 @@ class ParallelMixers(Mixer):
             raise ValueError("side-by-side mixers add their mean into the stream themselves")
         self.ops.normed_mean_add(residual, outputs, self.weights, self.eps)
         return None
+
+
+@MIXERS.register("latent_attention")
+class LatentAttention(Mixer):
+    """Softmax attention whose keys and values of all heads come from one small latent per
+    token. Parameters: ``hidden``, ``heads``, ``head_dim`` (unrotated query/key dimensions of a
+    head), ``rot_dim`` (rotated ones), ``value_dim``, ``latent`` (size of the latent), ``eps`` (of
+    the latent's norm), ``position`` (a position-encoding PartSpec for the rotated part), ``scale``,
+    ``gate`` (a sigmoid gate on the heads' outputs, computed from the mixer's input).
+
+    q = W_q x, head by head [head_dim unrotated | rot_dim rotated]. W_down x has latent + rot_dim
+    rows: the first ``latent``, divided by their root mean square and multiplied by ``down_norm``,
+    are the latent c; the last rot_dim are one rotated key part r that all heads share. Per head
+    h the key is [W_uk,h c | r] and the value W_uv,h c; causal softmax(q k^T scale) v; the heads
+    side by side are multiplied by sigmoid(W_g x) and projected by W_o.
+
+    Only c and r are kept per token: one row [c | r] in single-plane pages. The up-projections
+    move to the query's side: q_h . (W_uk,h c) = (W_uk,h^T q_h) . c, so every head's query becomes
+    [W_uk,h^T q_h | rotated part] against the one shared row, the attention's output is the
+    weights' average of c, and the head's value is W_uv,h applied to that average. Scores,
+    weights, the norm and the rotation are 32-bit."""
+
+    @classmethod
+    def tensors(cls, spec):
+        hidden, heads, latent = spec["hidden"], spec["heads"], spec["latent"]
+        inner = heads * spec["value_dim"]
+        out = {"q": TensorSpec((heads * (spec["head_dim"] + spec["rot_dim"]), hidden)),
+               "down": TensorSpec((latent + spec["rot_dim"], hidden)),
+               "down_norm": TensorSpec((latent,), "norm"),
+               "up_k": TensorSpec((heads * spec["head_dim"], latent)),
+               "up_v": TensorSpec((inner, latent)),
+               "out": TensorSpec((hidden, inner))}
+        if spec.get("gate", True):
+            out["gate"] = TensorSpec((inner, hidden))
+        return out
+
+    @classmethod
+    def cache_need(cls, spec):
+        return PagedKeyValues(1, spec["latent"] + spec["rot_dim"], planes=1)
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.heads, self.head_dim, self.rot_dim = spec["heads"], spec["head_dim"], spec["rot_dim"]
+        self.value_dim, self.latent = spec["value_dim"], spec["latent"]
+        self.scale, self.eps = float(spec["scale"]), float(spec["eps"])
+        position: PartSpec = spec.get("position") or PartSpec("none")
+        self.position = POSITIONS.get(position.kind)(position, {}, runtime)
+        self.neighbours = getattr(self.position, "layout", "halves") == "neighbours"
+        self.gated = bool(spec.get("gate", True))
+        # one product for everything that reads x: q | latent and shared key part | gate
+        names = ["q", "down"] + (["gate"] if self.gated else [])
+        self.project = self.matrix(torch.cat([tensors[name] for name in names], dim=0))
+        self.down_norm = self.vector(tensors["down_norm"])
+        # per head: [latent, head_dim] (the key's up-projection, transposed) and [value_dim, latent]
+        up_k = tensors["up_k"].view(self.heads, self.head_dim, self.latent)
+        self.up_k = self.matrix(up_k.transpose(1, 2))
+        self.up_v = self.matrix(tensors["up_v"].view(self.heads, self.value_dim, self.latent))
+        self.out = self.matrix(tensors["out"])
+        self.ops.check_attention_sizes(self.heads, 1, self.latent + self.rot_dim)
+
+    def inner_parts(self):
+        return (self.position,)
+
+    def forward(self, x, ctx, cache, write):
+        heads, latent, rot = self.heads, self.latent, self.rot_dim
+        projected = self.ops.linear(x, self.project)
+        tokens = projected.shape[0]
+        queries = torch.empty((tokens, heads, latent + rot), dtype=projected.dtype,
+                              device=projected.device)
+        # the latent's norm, the rotation of the shared key part and of the queries' rotated
+        # parts, the row [c | r] appended to the request's pages
+        self.ops.latent_prepare(projected, queries, heads=heads, head_dim=self.head_dim,
+                                rot_dim=rot, latent=latent, norm_weight=self.down_norm,
+                                eps=self.eps, rotary=self.position.rotary_table(),
+                                neighbours=self.neighbours, ctx=ctx, view=cache, write=write)
+        plain = projected[:, :heads * (self.head_dim + rot)].view(tokens, heads, -1)
+        self.ops.linear_heads(plain[:, :, :self.head_dim], self.up_k, out=queries[:, :, :latent])
+        mixed = self.ops.latent_attention(queries, heads=heads, latent=latent, scale=self.scale,
+                                          ctx=ctx, view=cache)
+        values = self.ops.linear_heads(mixed[:, :, :latent], self.up_v)
+        values = values.view(tokens, heads * self.value_dim)
+        if self.gated:
+            gate = projected[:, heads * (self.head_dim + rot) + latent + rot:]
+            values = self.ops.sigmoid_gate(values, gate)
+        return self.ops.linear(values, self.out)
+
+
+@MIXERS.register("differential_attention")
+class DifferentialAttention(Mixer):
+    """Grouped-query attention with two score maps per head over the same values. Parameters:
+    ``hidden``, ``heads``, ``kv_heads``, ``head_dim`` (of one map's queries and keys),
+    ``value_dim``, ``eps``, ``scale``, ``diff`` (a constant of the mixing factor), ``chunk`` (None:
+    every earlier position is seen; else only those of the query's own chunk of ``chunk``
+    positions, counted from 0).
+
+    q = W_q x has heads * 2 * head_dim rows, k = W_k x kv_heads * 2 * head_dim, head by head as
+    [map 1 | map 2]; v = W_v x. Queries and keys are divided by their root mean square per head and
+    map and multiplied by ``q_norm`` / ``k_norm`` [head_dim]; no rotation. Each map is a causal
+    softmax attention of its own; with a1, a2 their outputs and lambda = exp(lq1 . lk1) -
+    exp(lq2 . lk2) + diff (one number), o = a1 - lambda a2, divided by its root mean square over
+    value_dim, times (1 - diff); W_o on the heads side by side.
+
+    The two maps run as twice as many heads of one attention: the rows of W_q and W_k are put
+    map by map at load time (query head m * heads + h, key head m * kv_heads + g), so that the
+    grouping of query heads over key heads holds within each map, and W_v is stacked twice so that
+    both maps' key heads find their values in the pages."""
+
+    @classmethod
+    def tensors(cls, spec):
+        hidden, dim = spec["hidden"], spec["head_dim"]
+        out = {"q": TensorSpec((spec["heads"] * 2 * dim, hidden)),
+               "k": TensorSpec((spec["kv_heads"] * 2 * dim, hidden)),
+               "v": TensorSpec((spec["kv_heads"] * spec["value_dim"], hidden)),
+               "q_norm": TensorSpec((dim,), "norm"), "k_norm": TensorSpec((dim,), "norm"),
+               "out": TensorSpec((hidden, spec["heads"] * spec["value_dim"]))}
+        for name in ("lq1", "lk1", "lq2", "lk2"):
+            out[name] = TensorSpec((dim,), "wide")
+        return out
+
+    @classmethod
+    def cache_need(cls, spec):
+        return PagedKeyValues(2 * spec["kv_heads"], max(spec["head_dim"], spec["value_dim"]),
+                              chunk=spec.get("chunk"))
+
+    @staticmethod
+    def _by_map(weight, heads, dim):
+        """Rows [head][map][dim] -> [map][head][dim]."""
+        return weight.view(heads, 2, dim, -1).transpose(0, 1).reshape(2 * heads * dim, -1)
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.heads, self.kv_heads = spec["heads"], spec["kv_heads"]
+        self.head_dim, self.value_dim = spec["head_dim"], spec["value_dim"]
+        if self.heads % self.kv_heads:
+            raise ValueError("heads must be a multiple of kv_heads")
+        self.row_dim = max(self.head_dim, self.value_dim)
+        self.scale, self.eps = float(spec["scale"]), float(spec["eps"])
+        self.diff = float(spec["diff"])
+        self.chunk = spec.get("chunk")
+        self.qkv = self.matrix(torch.cat([
+            self._by_map(tensors["q"], self.heads, self.head_dim),
+            self._by_map(tensors["k"], self.kv_heads, self.head_dim),
+            tensors["v"], tensors["v"]], dim=0))
+        self.q_norm = self.vector(tensors["q_norm"])
+        self.k_norm = self.vector(tensors["k_norm"])
+        dot = lambda a, b: (tensors[a].to(torch.float32) * tensors[b].to(torch.float32)).sum()
+        self.mix = float(torch.exp(dot("lq1", "lk1")) - torch.exp(dot("lq2", "lk2"))) + self.diff
+        self.out = self.matrix(tensors["out"])
+        self.ops.check_attention_sizes(2 * self.heads, 2 * self.kv_heads, self.row_dim)
+        self.extra = {}
+        if self.value_dim != self.head_dim:
+            self.extra = dict(value_dim=self.value_dim, amplitude=1.0, norm_after=False)
+
+    def forward(self, x, ctx, cache, write):
+        qkv = self.ops.linear(x, self.qkv)
+        maps = self.ops.qkv_attention(
+            qkv, heads=2 * self.heads, kv_heads=2 * self.kv_heads, head_dim=self.head_dim,
+            q_weight=self.q_norm, k_weight=self.k_norm, eps=self.eps, rotary=None,
+            scale=self.scale, window=None, chunk=self.chunk, ctx=ctx, view=cache, write=write,
+            **self.extra)
+        mixed = self.ops.differential_combine(maps, heads=self.heads, row_dim=self.row_dim,
+                                              value_dim=self.value_dim, mix=self.mix, eps=self.eps,
+                                              factor=1.0 - self.diff)
+        return self.ops.linear(mixed, self.out)

@@ -7,7 +7,7 @@ from typing import Any, Mapping
 import torch
 
 from .base import Runtime, StepContext
-from .registry import BLOCKS, FEED_FORWARDS, MIXERS, NORMS
+from .registry import BLOCKS, EMBEDDINGS, FEED_FORWARDS, MIXERS, NORMS
 from .spec import LayerCall, ModelSpec, PartSpec, TensorSpec
 
 
@@ -26,6 +26,8 @@ def expected_tensors(spec: ModelSpec) -> dict[str, TensorSpec]:
             if part is not None:
                 out.update(_part_tensors(registry, part, layer.prefix))
     out.update(_part_tensors(NORMS, spec.final_norm, ""))
+    if spec.embedding_part is not None:
+        out.update(_part_tensors(EMBEDDINGS, spec.embedding_part, ""))
     out.update(spec.vectors)
     if spec.head is not None:
         out[spec.head] = TensorSpec((spec.vocab_size, spec.hidden_size))
@@ -38,15 +40,29 @@ def entry_key(entry: int, name: str | None = None):
     return entry if name is None else (entry, name)
 
 
+# what a block keeps for itself is stored beside its mixer's cache, under names that begin so
+BLOCK_PREFIX = "block:"
+# the cache entry of the embedding part
+EMBEDDING_ENTRY = (-1, "embedding")
+
+
 def _needs_of(spec: ModelSpec, call: LayerCall, index: int) -> dict[Any, Any]:
     entry = index if call.cache is None else call.cache
     layer = spec.layers[call.layer]
+    out: dict[Any, Any] = {}
+    own = BLOCKS.get(layer.block.kind).cache_need(layer.block)
+    for name, part in (own or {}).items():
+        if part is not None:
+            out[entry_key(entry, BLOCK_PREFIX + name)] = part
     need = MIXERS.get(layer.mixer.kind).cache_need(layer.mixer)
     if need is None:
-        return {}
+        return out
     if isinstance(need, Mapping):
-        return {entry_key(entry, name): part for name, part in need.items() if part is not None}
-    return {entry: need}
+        out.update({entry_key(entry, name): part for name, part in need.items()
+                    if part is not None})
+    else:
+        out[entry] = need
+    return out
 
 
 def cache_entries(spec: ModelSpec) -> dict[Any, Any]:
@@ -69,6 +85,10 @@ def cache_entries(spec: ModelSpec) -> dict[Any, Any]:
                 raise ValueError(f"call {index} reads cache entry {key} that nothing writes")
             if needs[key] != need:
                 raise ValueError(f"call {index} reads cache entry {key} of another shape")
+    if spec.embedding_part is not None:
+        need = EMBEDDINGS.get(spec.embedding_part.kind).cache_need(spec.embedding_part)
+        if need is not None:
+            needs[EMBEDDING_ENTRY] = need
     return needs
 
 
@@ -78,8 +98,14 @@ def view_of(views: Mapping[Any, Any], entry: int):
     if entry in views:
         return views[entry]
     named = {key[1]: view for key, view in views.items()
-             if isinstance(key, tuple) and key[0] == entry}
+             if isinstance(key, tuple) and key[0] == entry and not key[1].startswith(BLOCK_PREFIX)}
     return named or None
+
+
+def block_view_of(views: Mapping[Any, Any], entry: int):
+    """What a call's block gets as ``own_cache``: a dict name -> view of what it keeps itself."""
+    return {key[1][len(BLOCK_PREFIX):]: view for key, view in views.items()
+            if isinstance(key, tuple) and key[0] == entry and key[1].startswith(BLOCK_PREFIX)}
 
 
 class Model:
@@ -102,6 +128,10 @@ class Model:
             return cls(part, local, runtime, **extra)
 
         self.embedding = tensors[spec.embedding].to(runtime.dtype).contiguous()
+        self.embedding_part = None
+        if spec.embedding_part is not None:
+            self.embedding_part = build(EMBEDDINGS, spec.embedding_part, "")
+            self.embedding = self.embedding_part.table
         self.layers = []
         for layer in spec.layers:
             roles = dict(
@@ -148,7 +178,12 @@ class Model:
             parts += [part for part in (block, block.mixer, block.mixer_norm, block.feed_forward,
                                         block.feed_forward_norm) if part is not None]
             parts += list(getattr(block.mixer, "inner_parts", lambda: ())())
+        if self.embedding_part is not None:
+            parts.append(self.embedding_part)
         self.capturable = all(getattr(part, "capturable", True) for part in parts)
+        # blocks that read the streams of the calls before them (see Block.keeps_streams)
+        self.keeps_streams = any(block.keeps_streams for block in self.layers)
+        self.own_caches = [bool(type(block).cache_need(block.spec)) for block in self.layers]
         # For debugging: called as observer(place, residual, delta) after the embedding
         # (place -1) and after every call of a layer (place = its number in the order); the
         # hidden state there is residual + s * delta, s the block's ``pending_scale`` (1 unless the
@@ -158,7 +193,21 @@ class Model:
         self.observer = None
 
     def forward(self, ctx: StepContext):
-        residual = self.ops.embedding(ctx.token_ids, self.embedding)
+        kept = None
+        if self.keeps_streams:
+            # the embedding's output, every call's result, and what the last call passes on
+            kept = torch.empty((len(self.order) + 2, ctx.tokens, self.spec.hidden_size),
+                               dtype=torch.float32, device=self.runtime.device)
+        if self.embedding_part is not None:
+            residual = self.embedding_part.forward(
+                ctx, ctx.views.get(EMBEDDING_ENTRY), None if kept is None else kept[0])
+        else:
+            residual = self.ops.embedding(ctx.token_ids, self.embedding)
+            if kept is not None:
+                kept[0].copy_(residual)
+        if kept is not None:
+            # the first call works on a copy: the embedding's output is read again later
+            residual = self.ops.stream_average(kept, None, 1, kept[1])
         delta, scale = None, 1.0
         if self.observer is not None:
             self.observer(-1, residual, delta)
@@ -181,8 +230,17 @@ class Model:
                                      self.injected.get(place), **extra)
                 delta, extra = None, {}
             block = self.layers[call.layer]
-            delta = block.forward(residual, delta, ctx, view_of(ctx.views, call.cache),
-                                  call.writes_cache, **extra)
+            if self.own_caches[call.layer]:
+                extra["own_cache"] = block_view_of(ctx.views, call.cache)
+            if block.keeps_streams:
+                residual, delta = block.forward(
+                    residual, delta, ctx, view_of(ctx.views, call.cache), call.writes_cache,
+                    streams=(kept, place), **extra)
+            else:
+                delta = block.forward(residual, delta, ctx, view_of(ctx.views, call.cache),
+                                      call.writes_cache, **extra)
+                if kept is not None:
+                    raise ValueError("a model that keeps its streams has blocks that all do")
             scale = block.pending_scale
             if self.observer is not None:
                 self.observer(place, residual, delta)

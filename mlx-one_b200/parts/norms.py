@@ -35,3 +35,8 @@ class RMSNorm(Norm):
             return self.ops.add_rmsnorm(residual, delta, self.weight, self.eps, self.runtime.dtype)
         return self.ops.add_rmsnorm(residual, delta, self.weight, self.eps, self.runtime.dtype,
                                     delta_scale=delta_scale)
+
+    def add_normed(self, residual, x):
+        """In place: residual += x * rsqrt(mean(x^2) + eps) * weight, the norm taken over a part's
+        output ``x`` (compute dtype) and everything in 32-bit."""
+        self.ops.normed_mean_add(residual, [x], [self.weight], self.eps)

@@ -1,4 +1,5 @@
-"""Registries of part kinds: mixers, feed-forwards, norms, position encodings, blocks.
+"""Registries of part kinds: mixers, feed-forwards, norms, position encodings, blocks,
+embeddings.
 
 A part is a class registered under a kind name. Every part class provides
 
@@ -10,7 +11,8 @@ A part is a class registered under a kind name. Every part class provides
 Mixers add ``cache_need(spec)`` (classmethod) and ``forward(x, ctx, cache, write)``;
 feed-forwards add ``forward(x, ctx)``; norms add ``forward(residual, delta)``;
 position encodings add ``rotary_table()``; blocks add ``forward(residual, delta, ctx,
-cache, write)``. The signatures are written out in ``parts/base.py``.
+cache, write)``; embeddings add ``cache_need(spec)`` and ``forward(ctx, cache, out)``. The
+signatures are written out in ``parts/base.py``.
 """
 
 from __future__ import annotations
@@ -48,3 +50,4 @@ FEED_FORWARDS = PartRegistry("feed-forward")
 NORMS = PartRegistry("norm")
 POSITIONS = PartRegistry("position encoding")
 BLOCKS = PartRegistry("block")
+EMBEDDINGS = PartRegistry("embedding")

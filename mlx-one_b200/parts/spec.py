@@ -104,3 +104,6 @@ class ModelSpec:
     vectors: Mapping[str, Any] = field(default_factory=dict)
     # logits become cap * tanh(logits / cap); None: the output product's values as they are
     logit_softcap: float | None = None
+    # an embedding part (registry EMBEDDINGS) that makes the stream's first value; None: row
+    # ``token`` of the table ``embedding``. Its table is stored under ``embedding`` all the same.
+    embedding_part: PartSpec | None = None

@@ -151,12 +151,13 @@ class PlainOps:
         return q.contiguous()
 
     def qkv_attention(self, qkv, *, heads, kv_heads, head_dim, q_weight, k_weight, eps, rotary,
-                      scale, window, ctx, view, write, sinks=None, **extra):
+                      scale, window, ctx, view, write, sinks=None, chunk=None, **extra):
         q = self.qk_norm_rope_store(qkv, heads=heads, kv_heads=kv_heads, head_dim=head_dim,
                                     q_weight=q_weight, k_weight=k_weight, eps=eps, rotary=rotary,
                                     ctx=ctx, view=view, write=write, **extra)
         return self.paged_attention(q, heads=heads, kv_heads=kv_heads, head_dim=view.kv.shape[-1],
-                                    scale=scale, window=window, ctx=ctx, view=view, sinks=sinks)
+                                    scale=scale, window=window, ctx=ctx, view=view, sinks=sinks,
+                                    chunk=chunk)
 
     def concat_stream(self, residual, delta, token_ids, table, dtype, delta_scale=1.0):
         stream = residual if delta is None else residual + delta.float() * delta_scale
@@ -216,9 +217,13 @@ class PlainOps:
         if vector is not None:
             residual += vector
 
-    def activation(self, x, kind):
+    def activation(self, x, kind, params=None):
         z = x.float()
-        if kind == "relu2":
+        if kind == "xielu":
+            above, below = params
+            out = torch.where(z > 0, above * z * z + 0.5 * z,
+                              below * (torch.expm1(torch.clamp(z, max=0.0)) - z) + 0.5 * z)
+        elif kind == "relu2":
             out = torch.relu(z) ** 2
         elif kind == "relu":
             out = torch.relu(z)
@@ -230,8 +235,127 @@ class PlainOps:
             raise ValueError(kind)
         return out.to(x.dtype)
 
-    def linear_act(self, a, w, kind):
-        return self.activation(self.linear(a, w), kind)
+    def linear_act(self, a, w, kind, params=None):
+        return self.activation(self.linear(a, w), kind, params)
+
+    # ---- the stream's first value, the streams kept over the layers, convolutions over time
+
+    def embedding_pairs(self, ids, table, scale, pairs, *, rule, ctx, view, out=None):
+        x = table[ids.long()].float() * scale
+        if pairs is not None:
+            buckets, mul_prev, mul_cur = rule
+            tokens = ids.tolist()
+            starts, slots = ctx.request_start.tolist(), view.slots.tolist()
+            rows = []
+            for r in range(ctx.requests):
+                before = int(view.state[slots[r], 0]) - 1          # -1: the sequence starts here
+                for t in range(starts[r], starts[r + 1]):
+                    rows.append(buckets if before < 0
+                                else (before * mul_prev + tokens[t] * mul_cur) % buckets)
+                    before = tokens[t]
+                view.state[slots[r], 0] = before + 1
+            x = x + pairs[torch.tensor(rows, dtype=torch.long)].float()
+        if out is None:
+            return x
+        out.copy_(x)
+        return out
+
+    def stream_average(self, kept, weights, count, out):
+        if weights is None:
+            out.copy_(kept[0])
+        else:
+            out.copy_((kept[:count] * weights[:count, None, None]).sum(dim=0))
+        return out
+
+    def stream_conv(self, residual, kernel, *, taps, ctx, view, sublayer, write, dtype):
+        if kernel is None or taps < 1:
+            return residual.to(dtype)
+        out = torch.empty_like(residual)
+        starts = ctx.request_start.tolist()
+        slots = view.slots.tolist() if view is not None else None
+        for r in range(ctx.requests):
+            first, last = starts[r], starts[r + 1]
+            n = last - first
+            rows = residual[first:last]
+            if taps > 1:
+                state = view.state[slots[r], sublayer]                 # [taps - 1, hidden]
+                padded = torch.cat((state, rows), dim=0)
+            else:
+                padded = rows
+            y = rows.clone()
+            for j in range(taps):
+                y = y + padded[j:j + n] * kernel[:, j]
+            out[first:last] = y
+            if write and taps > 1:
+                view.state[slots[r], sublayer] = padded[n:n + taps - 1]
+        return out.to(dtype)
+
+    # ---- attention over one latent row per token
+
+    def latent_prepare(self, projected, queries, *, heads, head_dim, rot_dim, latent, norm_weight,
+                       eps, rotary, neighbours, ctx, view, write):
+        tokens = projected.shape[0]
+        flat = projected.float()
+        per_head = head_dim + rot_dim
+        q_rot = flat[:, :heads * per_head].view(tokens, heads, per_head)[:, :, head_dim:]
+        down = flat[:, heads * per_head:heads * per_head + latent + rot_dim]
+        c = down[:, :latent]
+        c = c * torch.rsqrt(c.pow(2).mean(dim=-1, keepdim=True) + eps) * norm_weight
+        shared = down[:, latent:]
+
+        def rotate(x):
+            if rotary is None:
+                return x
+            inv_freq, dims = rotary
+            angles = ctx.positions.float()[:, None] * inv_freq[None, :]
+            cos, sin = torch.cos(angles), torch.sin(angles)
+            if x.dim() == 3:
+                cos, sin = cos[:, None, :], sin[:, None, :]
+            out = x.clone()
+            if neighbours:
+                a, b = x[..., 0:dims:2], x[..., 1:dims:2]
+                out[..., 0:dims:2] = a * cos - b * sin
+                out[..., 1:dims:2] = b * cos + a * sin
+            else:
+                half = dims // 2
+                a, b = x[..., :half], x[..., half:dims]
+                out[..., :half] = a * cos - b * sin
+                out[..., half:dims] = b * cos + a * sin
+            return out
+
+        queries[:, :, latent:] = rotate(q_rot).to(queries.dtype)
+        row = torch.cat((c, rotate(shared)), dim=1).to(view.kv.dtype)
+        if write:
+            positions, requests = ctx.positions.tolist(), ctx.token_request.tolist()
+            table = view.block_table.tolist()
+            for t in range(tokens):
+                page = table[requests[t]][positions[t] // view.page_size]
+                assert page >= 0, "a row is written to a position without a page"
+                view.kv[0, page, 0, positions[t] % view.page_size] = row[t]
+
+    def linear_heads(self, a, w, out=None):
+        """a [tokens, heads, K] (rows may be slices) with w [heads, N, K] -> [tokens, heads, N]."""
+        result = torch.einsum("thk,hnk->thn", a.float(), w.float()).to(a.dtype).contiguous()
+        if out is None:
+            return result
+        out.copy_(result)
+        return out
+
+    def latent_attention(self, queries, *, heads, latent, scale, ctx, view):
+        tokens, _, row = queries.shape
+        flat = self.paged_attention(queries, heads=heads, kv_heads=1, head_dim=row, scale=scale,
+                                    window=None, ctx=ctx, view=view)
+        return flat.view(tokens, heads, row)
+
+    def sigmoid_gate(self, values, gate):
+        return (values.float() * torch.sigmoid(gate.float())).to(values.dtype)
+
+    def differential_combine(self, maps, *, heads, row_dim, value_dim, mix, eps, factor):
+        tokens = maps.shape[0]
+        both = maps.float().view(tokens, 2, heads, row_dim)[..., :value_dim]
+        o = both[:, 0] - torch.tensor(mix, dtype=torch.float32) * both[:, 1]
+        o = o * torch.rsqrt(o.pow(2).mean(dim=-1, keepdim=True) + eps) * factor
+        return o.reshape(tokens, heads * value_dim).to(maps.dtype)
 
     def normed_mean_add(self, residual, outputs, weights, eps):
         total = torch.zeros_like(residual)
@@ -288,7 +412,7 @@ class PlainOps:
         return out.reshape(tokens, inner).to(projected.dtype)
 
     def paged_attention(self, q, *, heads, kv_heads, head_dim, scale, window, ctx, view,
-                        sinks=None):
+                        sinks=None, chunk=None):
         tokens = q.shape[0]
         out = torch.empty(tokens, heads, head_dim)
         positions = ctx.positions.tolist()
@@ -298,12 +422,14 @@ class PlainOps:
         for t in range(tokens):
             p = positions[t]
             lowest = max(p - window + 1, 0) if window else 0
+            if chunk:
+                lowest = max(lowest, p - p % chunk)
             keys = list(range(lowest, p + 1))
             pages = [table[requests[t]][key // view.page_size] for key in keys]
             assert min(pages) >= 0, "a key is read from a position without a page"
             offsets = [key % view.page_size for key in keys]
             k = view.kv[0, pages, :, offsets].float()            # [keys, kv_heads, head_dim]
-            v = view.kv[1, pages, :, offsets].float()
+            v = view.kv[view.kv.shape[0] - 1, pages, :, offsets].float()
             k = k.repeat_interleave(group, dim=1)
             v = v.repeat_interleave(group, dim=1)
             scores = torch.einsum("hd,khd->hk", q[t].float(), k) * scale
