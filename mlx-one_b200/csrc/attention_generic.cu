@@ -104,12 +104,15 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ kv,
 
 }  // namespace
 
-MLXONE_API int mlxone_attention_generic(const void* q, const void* kv, const int* block_table,
-                                        int table_width, int page_size, int pages,
-                                        const int* positions, const int* token_request, void* out,
-                                        int tokens, int heads, int kv_heads, int head_dim,
-                                        float scale, int window, int dtype, const float* sinks,
-                                        int* error_flag, cudaStream_t stream) {
+// `planes`: 2 = values lie in a second plane behind all keys' pages; 1 = a token's row is its key
+// and its value.
+MLXONE_API int mlxone_attention_generic_planes(const void* q, const void* kv,
+                                               const int* block_table, int table_width,
+                                               int page_size, int pages, const int* positions,
+                                               const int* token_request, void* out, int tokens,
+                                               int heads, int kv_heads, int head_dim, float scale,
+                                               int window, int dtype, const float* sinks,
+                                               int planes, int* error_flag, cudaStream_t stream) {
     if (tokens == 0) return 0;
     MLXONE_REQUIRE(tokens > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
                    "attention: %d heads cannot share %d key heads", heads, kv_heads);
@@ -119,7 +122,8 @@ MLXONE_API int mlxone_attention_generic(const void* q, const void* kv, const int
     const long long items = (long long)tokens * heads;
     const int blocks = ceil_div_host(items, WARPS);
     const size_t shared = (size_t)WARPS * head_dim * sizeof(float);
-    const long long kv_half = (long long)pages * kv_heads * page_size * head_dim;
+    MLXONE_REQUIRE(planes == 1 || planes == 2, "attention: one or two planes, not %d", planes);
+    const long long kv_half = planes == 1 ? 0 : (long long)pages * kv_heads * page_size * head_dim;
     if (dtype == MLXONE_BF16) {
         using T = __nv_bfloat16;
         attention_generic_kernel<T><<<blocks, WARPS * 32, shared, stream>>>(
@@ -135,4 +139,16 @@ MLXONE_API int mlxone_attention_generic(const void* q, const void* kv, const int
     }
     MLXONE_LAUNCH_CHECK("attention_generic");
     return 0;
+}
+
+MLXONE_API int mlxone_attention_generic(const void* q, const void* kv, const int* block_table,
+                                        int table_width, int page_size, int pages,
+                                        const int* positions, const int* token_request, void* out,
+                                        int tokens, int heads, int kv_heads, int head_dim,
+                                        float scale, int window, int dtype, const float* sinks,
+                                        int* error_flag, cudaStream_t stream) {
+    return mlxone_attention_generic_planes(q, kv, block_table, table_width, page_size, pages,
+                                           positions, token_request, out, tokens, heads, kv_heads,
+                                           head_dim, scale, window, dtype, sinks, 2, error_flag,
+                                           stream);
 }

@@ -56,16 +56,29 @@ template <typename T>
 __device__ __forceinline__ float round_to(float v) { return to_float<T>(from_float<T>(v)); }
 
 // Activations of a feed-forward without a gate, by the code the C interface uses.
-enum : int { MLXONE_ACT_RELU2 = 0, MLXONE_ACT_GELU_TANH = 1, MLXONE_ACT_SILU = 2, MLXONE_ACT_RELU = 3 };
+// xielu has two numbers a and b: a z^2 + z / 2 above zero, b (e^z - 1 - z) + z / 2 at and below it.
+enum : int { MLXONE_ACT_RELU2 = 0, MLXONE_ACT_GELU_TANH = 1, MLXONE_ACT_SILU = 2, MLXONE_ACT_RELU = 3,
+             MLXONE_ACT_XIELU = 4 };
 
-__device__ __forceinline__ float mlxone_activate(float z, int kind) {
+__device__ __forceinline__ float mlxone_activate(float z, int kind, float a = 0.f, float b = 0.f) {
     switch (kind) {
+        case MLXONE_ACT_XIELU:
+            return z > 0.f ? fmaf(a * z, z, 0.5f * z) : fmaf(b, expf(z) - 1.f - z, 0.5f * z);
         case MLXONE_ACT_RELU2: { const float r = fmaxf(z, 0.f); return r * r; }
         case MLXONE_ACT_GELU_TANH:
             return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
         case MLXONE_ACT_SILU: return z / (1.f + expf(-z));
         default: return fmaxf(z, 0.f);
     }
+}
+
+// The first key that a query at `position` reads; the last one is its own. span > 0: a sliding
+// window of that many keys. span < 0: chunks of -span positions counted from 0, a query reads
+// the keys of its own chunk. 0: every earlier key. The result never falls as the position grows.
+__host__ __device__ __forceinline__ int first_visible_key(int position, int span) {
+    if (span > 0) return position - span + 1 > 0 ? position - span + 1 : 0;
+    if (span < 0) return position - position % (-span);
+    return 0;
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

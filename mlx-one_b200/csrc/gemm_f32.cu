@@ -14,7 +14,13 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const float* __restrict__
                                                        const float* __restrict__ w, int ldw,
                                                        const float* __restrict__ bias,
                                                        float* __restrict__ out, int ldo, int m,
-                                                       int n, int k) {
+                                                       int n, int k, long long batch_a,
+                                                       long long batch_w, long long batch_out) {
+    // (blockIdx.z: one of several products of the same shape whose operands lie a fixed number
+    // of values apart)
+    a += blockIdx.z * batch_a;
+    w += blockIdx.z * batch_w;
+    out += blockIdx.z * batch_out;
     __shared__ float as[BK][BM + 4];
     __shared__ float ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -93,9 +99,35 @@ MLXONE_API int mlxone_gemm_f32(const float* a, int lda, const float* w, int ldw,
                      (reinterpret_cast<uintptr_t>(a) & 15) == 0 &&
                      (reinterpret_cast<uintptr_t>(w) & 15) == 0;
     if (vec)
-        gemm_f32_kernel<true><<<grid, 256, 0, stream>>>(a, lda, w, ldw, bias, out, ldo, m, n, k);
+        gemm_f32_kernel<true><<<grid, 256, 0, stream>>>(a, lda, w, ldw, bias, out, ldo, m, n, k, 0, 0, 0);
     else
-        gemm_f32_kernel<false><<<grid, 256, 0, stream>>>(a, lda, w, ldw, bias, out, ldo, m, n, k);
+        gemm_f32_kernel<false><<<grid, 256, 0, stream>>>(a, lda, w, ldw, bias, out, ldo, m, n, k, 0, 0, 0);
     MLXONE_LAUNCH_CHECK("gemm_f32");
+    return 0;
+}
+
+// `batch` products of one shape: product b reads a + b * batch_a and w + b * batch_w and writes
+// out + b * batch_out (distances in values). A head-by-head product over rows that hold all
+// heads side by side is this with batch_a = the head's width and lda = the row's.
+MLXONE_API int mlxone_gemm_f32_batched(const float* a, int lda, long long batch_a, const float* w,
+                                       int ldw, long long batch_w, float* out, int ldo,
+                                       long long batch_out, int m, int n, int k, int batch,
+                                       cudaStream_t stream) {
+    if (m == 0 || n == 0 || batch == 0) return 0;
+    MLXONE_REQUIRE(m > 0 && n > 0 && k > 0 && batch > 0 && batch <= 65535,
+                   "gemm_f32_batched: bad sizes m=%d n=%d k=%d batch=%d", m, n, k, batch);
+    MLXONE_REQUIRE(lda >= k && ldw >= k && ldo >= n, "gemm_f32_batched: leading dimension too small");
+    const dim3 grid(ceil_div_host(n, BN), ceil_div_host(m, BM), batch);
+    MLXONE_REQUIRE(grid.y <= 65535, "gemm_f32_batched: too many rows (%d)", m);
+    const bool vec = k % 4 == 0 && lda % 4 == 0 && ldw % 4 == 0 && batch_a % 4 == 0 &&
+                     batch_w % 4 == 0 && (reinterpret_cast<uintptr_t>(a) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(w) & 15) == 0;
+    if (vec)
+        gemm_f32_kernel<true><<<grid, 256, 0, stream>>>(a, lda, w, ldw, nullptr, out, ldo, m, n, k,
+                                                        batch_a, batch_w, batch_out);
+    else
+        gemm_f32_kernel<false><<<grid, 256, 0, stream>>>(a, lda, w, ldw, nullptr, out, ldo, m, n, k,
+                                                         batch_a, batch_w, batch_out);
+    MLXONE_LAUNCH_CHECK("gemm_f32_batched");
     return 0;
 }

@@ -141,21 +141,24 @@ MLXONE_API int mlxone_gated_activation(const void* gate_up, void* out, int rows,
 }
 
 // ------------------------------------------------------------------ activations
-// (mlxone_activate in common.cuh: relu2, gelu_tanh, silu, relu)
-__device__ __forceinline__ float activate(float z, int kind) { return mlxone_activate(z, kind); }
+// (mlxone_activate in common.cuh: relu2, gelu_tanh, silu, relu, xielu with its two numbers)
+__device__ __forceinline__ float activate(float z, int kind, float a, float b) {
+    return mlxone_activate(z, kind, a, b);
+}
 
 template <typename T>
 __global__ void activation_kernel(const T* __restrict__ x, T* __restrict__ out, long long total,
-                                  int kind) {
+                                  int kind, float a, float b) {
     griddep_launch();
     griddep_wait();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < total) out[i] = from_float<T>(activate(to_float<T>(x[i]), kind));
+    if (i < total) out[i] = from_float<T>(activate(to_float<T>(x[i]), kind, a, b));
 }
 
 // bfloat16, eight values a thread
 __global__ void activation_wide_kernel(const __nv_bfloat16* __restrict__ x,
-                                       __nv_bfloat16* __restrict__ out, long long groups, int kind) {
+                                       __nv_bfloat16* __restrict__ out, long long groups, int kind,
+                                       float a, float b) {
     griddep_launch();
     griddep_wait();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -166,27 +169,35 @@ __global__ void activation_wide_kernel(const __nv_bfloat16* __restrict__ x,
     __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&packed);
 #pragma unroll
     for (int k = 0; k < 4; ++k)
-        q[k] = __floats2bfloat162_rn(activate(__low2float(in[k]), kind),
-                                     activate(__high2float(in[k]), kind));
+        q[k] = __floats2bfloat162_rn(activate(__low2float(in[k]), kind, a, b),
+                                     activate(__high2float(in[k]), kind, a, b));
     *reinterpret_cast<uint4*>(out + i * 8) = packed;
+}
+
+// `a` and `b`: the two numbers of an activation that has some (xielu), else ignored.
+MLXONE_API int mlxone_activation_shaped(const void* x, void* out, long long total, int kind,
+                                        float a, float b, int dtype, cudaStream_t stream) {
+    if (total == 0) return 0;
+    MLXONE_REQUIRE(total > 0 && kind >= 0 && kind <= 4, "activation: bad arguments");
+    if (dtype == MLXONE_BF16 && total % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+        (reinterpret_cast<uintptr_t>(out) & 15) == 0)
+        launch_kernel(activation_wide_kernel, dim3(ceil_div_host(total / 8, 256)), dim3(256), 0,
+                      stream, true, (const __nv_bfloat16*)x, (__nv_bfloat16*)out, total / 8, kind,
+                      a, b);
+    else if (dtype == MLXONE_BF16)
+        launch_kernel(activation_kernel<__nv_bfloat16>, dim3(ceil_div_host(total, 256)), dim3(256), 0,
+                      stream, true, (const __nv_bfloat16*)x, (__nv_bfloat16*)out, total, kind, a, b);
+    else
+        launch_kernel(activation_kernel<float>, dim3(ceil_div_host(total, 256)), dim3(256), 0, stream,
+                      true, (const float*)x, (float*)out, total, kind, a, b);
+    MLXONE_LAUNCH_CHECK("activation");
+    return 0;
 }
 
 MLXONE_API int mlxone_activation(const void* x, void* out, long long total, int kind, int dtype,
                                  cudaStream_t stream) {
-    if (total == 0) return 0;
-    MLXONE_REQUIRE(total > 0 && kind >= 0 && kind <= 3, "activation: bad arguments");
-    if (dtype == MLXONE_BF16 && total % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
-        (reinterpret_cast<uintptr_t>(out) & 15) == 0)
-        launch_kernel(activation_wide_kernel, dim3(ceil_div_host(total / 8, 256)), dim3(256), 0,
-                      stream, true, (const __nv_bfloat16*)x, (__nv_bfloat16*)out, total / 8, kind);
-    else if (dtype == MLXONE_BF16)
-        launch_kernel(activation_kernel<__nv_bfloat16>, dim3(ceil_div_host(total, 256)), dim3(256), 0,
-                      stream, true, (const __nv_bfloat16*)x, (__nv_bfloat16*)out, total, kind);
-    else
-        launch_kernel(activation_kernel<float>, dim3(ceil_div_host(total, 256)), dim3(256), 0, stream,
-                      true, (const float*)x, (float*)out, total, kind);
-    MLXONE_LAUNCH_CHECK("activation");
-    return 0;
+    MLXONE_REQUIRE(kind >= 0 && kind <= 3, "activation: bad arguments");
+    return mlxone_activation_shaped(x, out, total, kind, 0.f, 0.f, dtype, stream);
 }
 
 // ------------------------------------------------------------------ mean of normed branches

@@ -437,24 +437,33 @@ class CudaOps:
 
     # ---- activations of a feed-forward without a gate
 
-    ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
+    ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "relu": 3, "xielu": 4}
 
-    def activation(self, x, kind):
-        """relu2 (max(z, 0)^2), gelu_tanh, silu or relu of every value."""
+    def activation(self, x, kind, params=None):
+        """relu2 (max(z, 0)^2), gelu_tanh, silu, relu or xielu of every value. ``params``: the
+        two numbers (a, b) of xielu: a z^2 + z / 2 above zero, b (e^z - 1 - z) + z / 2 below."""
         if kind not in self.ACTIVATIONS:
             raise KernelError(f"unknown activation {kind!r}")
+        if (kind == "xielu") != (params is not None):
+            raise KernelError("xielu, and only xielu, takes two numbers")
         self._need(x, x.dtype, "x")
         out = torch.empty_like(x)
-        self._call("mlxone_activation", _c_void_p(_ptr(x)), _c_void_p(_ptr(out)),
-                   _c_ll(x.numel()), _c_int(self.ACTIVATIONS[kind]), _c_int(_dtype_code(x.dtype)))
+        a, b = params or (0.0, 0.0)
+        self._call("mlxone_activation_shaped", _c_void_p(_ptr(x)), _c_void_p(_ptr(out)),
+                   _c_ll(x.numel()), _c_int(self.ACTIVATIONS[kind]), _c_float(a), _c_float(b),
+                   _c_int(_dtype_code(x.dtype)))
         return out
 
-    def linear_act(self, a, w, kind):
+    def linear_act(self, a, w, kind, params=None):
         """act(a @ w^T): for few rows the activation is the skinny product's epilogue (also with
         the norm of its input applied while loading); else the product, then the activation
-        kernel."""
+        kernel. An activation with numbers of its own (``params``) is always the latter."""
         if kind not in self.ACTIVATIONS:
             raise KernelError(f"unknown activation {kind!r}")
+        if params is not None:
+            if isinstance(a, NormedInput):
+                a = a.materialize()
+            return self.activation(self.linear(a, w), kind, params)
         epilogue = self._ACTIVATE + self.ACTIVATIONS[kind]
         if isinstance(a, NormedInput):
             out = torch.empty((a.shape[0], w.shape[0]), dtype=a.dtype, device=self.device)
@@ -466,6 +475,170 @@ class CudaOps:
             self._skinny_call(a, w, None, out, w.shape[0], epilogue)
             return out
         return self.activation(self.linear(a, w), kind)
+
+    # ---- the stream's first value, the streams kept over the layers, convolutions over time
+
+    def embedding_pairs(self, ids, table, scale, pairs, *, rule, ctx, view, out=None):
+        """float32 [tokens, hidden]: the table's row times ``scale``, plus (with ``pairs``) the
+        row of the second table that the token and the one before it in its request choose;
+        ``view`` is the int32 slot per request that holds the last token seen plus one."""
+        self._need(ids, torch.int32, "token ids")
+        tokens, hidden = ids.numel(), table.shape[1]
+        if out is None:
+            out = torch.empty((tokens, hidden), dtype=torch.float32, device=self.device)
+        self._need(out, torch.float32, "out")
+        self._need(table, table.dtype, "table")
+        buckets = mul_prev = mul_cur = 0
+        state = slots = None
+        if pairs is not None:
+            self._need(pairs, table.dtype, "pairs")
+            buckets, mul_prev, mul_cur = rule
+            if pairs.shape != (buckets + 1, hidden):
+                raise KernelError("the pair table has one row per bucket and one more")
+            self._need(view.state, torch.int32, "state")
+            state, slots = view.state, view.slots
+        self._call("mlxone_embedding_pairs", _c_void_p(_ptr(ids)), _c_void_p(_ptr(table)),
+                   _c_float(scale), _c_void_p(_ptr(pairs)), _c_int(buckets), _c_ll(mul_prev),
+                   _c_ll(mul_cur), _c_void_p(_ptr(ctx.token_request)),
+                   _c_void_p(_ptr(ctx.request_start)), _c_void_p(_ptr(state)),
+                   _c_void_p(_ptr(slots)), _c_void_p(_ptr(out)), _c_int(tokens), _c_int(hidden),
+                   _c_int(table.shape[0]), _c_int(_dtype_code(table.dtype)),
+                   _c_void_p(_ptr(self.error_flag)))
+        return out
+
+    def stream_average(self, kept, weights, count, out):
+        """out = sum_j weights[j] * kept[j], j < count (32-bit, added in that order); without
+        weights a copy of kept[0]. ``out`` may be a stream of ``kept`` beyond ``count``."""
+        self._need(kept, torch.float32, "kept")
+        self._need(out, torch.float32, "out")
+        if weights is not None:
+            self._need(weights, torch.float32, "weights")
+            if weights.numel() < count or kept.shape[0] < count:
+                raise KernelError(f"{count} streams are averaged, fewer are given")
+        self._call("mlxone_stream_average", _c_void_p(_ptr(kept)), _c_ll(kept.stride(0)),
+                   _c_void_p(_ptr(weights)), _c_int(count), _c_void_p(_ptr(out)),
+                   _c_ll(out.numel()))
+        return out
+
+    def stream_conv(self, residual, kernel, *, taps, ctx, view, sublayer, write, dtype):
+        """What a sublayer reads of the 32-bit stream, in ``dtype``: x + its causal convolution
+        over time on every channel (``kernel`` [hidden, taps]), the taps - 1 rows before a step's
+        first token from row ``sublayer`` of the request's slot (``view``), where the step's last
+        rows are left; without a kernel the stream, rounded."""
+        self._need(residual, torch.float32, "residual")
+        tokens, hidden = residual.shape
+        out = torch.empty((tokens, hidden), dtype=dtype, device=self.device)
+        state = slots = None
+        stride = 0
+        if kernel is None or taps < 1:
+            kernel, taps = None, 0
+        else:
+            self._need(kernel, torch.float32, "kernel")
+            if kernel.shape != (hidden, taps):
+                raise KernelError("the convolution's weights are [hidden, taps]")
+            if taps > 1:
+                self._need(view.state, torch.float32, "state")
+                if view.state.shape[2:] != (taps - 1, hidden):
+                    raise KernelError("a slot keeps taps - 1 rows per sublayer")
+                state, slots, stride = view.state[0, sublayer], view.slots, view.state.stride(0)
+        self._call("mlxone_stream_conv", _c_void_p(_ptr(residual)), _c_void_p(_ptr(kernel)),
+                   _c_int(taps), _c_void_p(_ptr(ctx.token_request)),
+                   _c_void_p(_ptr(ctx.request_start)), _c_void_p(_ptr(state)), _c_ll(stride),
+                   _c_void_p(_ptr(slots)), _c_void_p(_ptr(out)), _c_int(tokens), _c_int(hidden),
+                   _c_int(1 if write else 0), _c_int(_dtype_code(dtype)))
+        return out
+
+    # ---- attention over one latent row per token; two score maps per head
+
+    def latent_prepare(self, projected, queries, *, heads, head_dim, rot_dim, latent, norm_weight,
+                       eps, rotary, neighbours, ctx, view, write):
+        """The rotated parts of the queries into ``queries[:, :, latent:]``; the token's row
+        [normed latent | rotated shared key part] into its request's pages."""
+        self._need_rows(projected, queries.dtype, "projected")
+        self._need(queries, queries.dtype, "queries")
+        self._need(norm_weight, torch.float32, "norm weight")
+        self._need(view.kv, queries.dtype, "pages")
+        row = latent + rot_dim
+        if queries.shape[1:] != (heads, row) or view.kv.shape[0] != 1 or \
+                view.kv.shape[2] != 1 or view.kv.shape[-1] != row:
+            raise KernelError("queries and pages hold rows of latent + rot_dim values")
+        inv_freq, rotary_dim = (None, 0) if rotary is None else rotary
+        self._call("mlxone_latent_prepare", _c_void_p(_ptr(projected)),
+                   _c_int(projected.stride(0)), _c_void_p(_ptr(queries)),
+                   _c_void_p(_ptr(norm_weight)), _c_float(eps), _c_void_p(_ptr(inv_freq)),
+                   _c_int(rotary_dim), _c_int(1 if neighbours else 0),
+                   _c_void_p(_ptr(ctx.positions)), _c_void_p(_ptr(ctx.token_request)),
+                   _c_void_p(_ptr(view.kv)), _c_void_p(_ptr(view.block_table)),
+                   _c_int(view.block_table.shape[1]), _c_int(view.page_size),
+                   _c_int(projected.shape[0]), _c_int(heads), _c_int(head_dim), _c_int(rot_dim),
+                   _c_int(latent), _c_int(1 if write else 0), _c_int(_dtype_code(queries.dtype)),
+                   _c_void_p(_ptr(self.error_flag)))
+
+    def linear_heads(self, a, w, out=None):
+        """a [tokens, heads, K] with w [heads, N, K] -> [tokens, heads, N], one product per head.
+        The rows of ``a`` and ``out`` may be slices of wider rows (values of a head together)."""
+        tokens, heads, k = a.shape
+        n = w.shape[1]
+        if w.shape != (heads, n, k) or a.stride(2) != 1 or a.dtype != w.dtype:
+            raise KernelError("head-by-head product: a [tokens, heads, K], w [heads, N, K]")
+        self._need(w, a.dtype, "w")
+        if out is None:
+            out = torch.empty((tokens, heads, n), dtype=a.dtype, device=self.device)
+        if out.shape != (tokens, heads, n) or out.stride(2) != 1 or out.dtype != a.dtype:
+            raise KernelError("head-by-head product: out [tokens, heads, N]")
+        if tokens == 0:
+            return out
+        if a.dtype == torch.float32:
+            self._call("mlxone_gemm_f32_batched", _c_void_p(_ptr(a)), _c_int(a.stride(0)),
+                       _c_ll(a.stride(1)), _c_void_p(_ptr(w)), _c_int(k), _c_ll(n * k),
+                       _c_void_p(_ptr(out)), _c_int(out.stride(0)), _c_ll(out.stride(1)),
+                       _c_int(tokens), _c_int(n), _c_int(k), _c_int(heads))
+        else:
+            torch.bmm(a.transpose(0, 1), w.transpose(1, 2), out=out.transpose(0, 1))
+        return out
+
+    def latent_attention(self, queries, *, heads, latent, scale, ctx, view):
+        """Causal softmax attention of queries [tokens, heads, row] over the one row per token in
+        the request's single-plane pages, which is key and value at once. Returns [tokens, heads,
+        row]; the first ``latent`` values of a row are the weights' average of the latents."""
+        tokens, _, row = queries.shape
+        self._need(queries, view.kv.dtype, "queries")
+        out = torch.empty((tokens, heads, row), dtype=queries.dtype, device=self.device)
+        self._call("mlxone_attention_generic_planes", _c_void_p(_ptr(queries)),
+                   _c_void_p(_ptr(view.kv)), _c_void_p(_ptr(view.block_table)),
+                   _c_int(view.block_table.shape[1]), _c_int(view.page_size),
+                   _c_int(view.kv.shape[1]), _c_void_p(_ptr(ctx.positions)),
+                   _c_void_p(_ptr(ctx.token_request)), _c_void_p(_ptr(out)), _c_int(tokens),
+                   _c_int(heads), _c_int(1), _c_int(row), _c_float(scale), _c_int(0),
+                   _c_int(_dtype_code(queries.dtype)), _c_void_p(None), _c_int(1),
+                   _c_void_p(_ptr(self.error_flag)))
+        return out
+
+    def sigmoid_gate(self, values, gate):
+        """values * sigmoid(gate); the gate's rows may be a slice of wider rows."""
+        self._need(values, values.dtype, "values")
+        self._need_rows(gate, values.dtype, "gate")
+        if gate.shape != values.shape:
+            raise KernelError("gate and values differ in shape")
+        out = torch.empty_like(values)
+        self._call("mlxone_sigmoid_gate", _c_void_p(_ptr(values)), _c_void_p(_ptr(gate)),
+                   _c_int(gate.stride(0)), _c_void_p(_ptr(out)), _c_int(values.shape[0]),
+                   _c_int(values.shape[1]), _c_int(_dtype_code(values.dtype)))
+        return out
+
+    def differential_combine(self, maps, *, heads, row_dim, value_dim, mix, eps, factor):
+        """maps [tokens, 2 * heads * row_dim] (map by map, the first value_dim values of a row
+        count) -> [tokens, heads * value_dim]: o = a1 - mix a2, o / rms(o) * factor, in 32-bit."""
+        self._need(maps, maps.dtype, "maps")
+        tokens = maps.shape[0]
+        if maps.shape[1] != 2 * heads * row_dim:
+            raise KernelError("the maps' width does not match the head count")
+        out = torch.empty((tokens, heads * value_dim), dtype=maps.dtype, device=self.device)
+        self._call("mlxone_differential_combine", _c_void_p(_ptr(maps)), _c_void_p(_ptr(out)),
+                   _c_int(tokens), _c_int(heads), _c_int(row_dim), _c_int(value_dim),
+                   _c_float(mix), _c_float(eps), _c_float(factor),
+                   _c_int(_dtype_code(maps.dtype)))
+        return out
 
     # ---- the 32-bit stream
 
@@ -810,8 +983,17 @@ class CudaOps:
                    _c_void_p(_ptr(self.error_flag)))
         return q
 
+    @staticmethod
+    def _span(window, chunk):
+        """What the attention kernels take as their window: a positive number of keys for a
+        sliding window, minus the chunk size for chunks of positions that see only themselves,
+        0 for every earlier key."""
+        if window and chunk:
+            raise KernelError("a window and chunks together are not implemented")
+        return -int(chunk) if chunk else int(window or 0)
+
     def qkv_attention(self, qkv, *, heads, kv_heads, head_dim, q_weight, k_weight, eps, rotary,
-                      scale, window, ctx, view, write, sinks=None, **extra):
+                      scale, window, ctx, view, write, sinks=None, chunk=None, **extra):
         """From the fused projection qkv [tokens, (heads + 2 kv_heads) * head_dim] to the mixed
         heads [tokens, heads * head_dim]: per-head norm of queries and keys, rotation, keys and
         values appended to the pages, attention. A step of single tokens in bfloat16 whose head
@@ -819,6 +1001,7 @@ class CudaOps:
         one kernel; everything else as the preparation kernel followed by attention."""
         tokens = qkv.shape[0]
         inv_freq, rotary_dim = (None, 0) if rotary is None else rotary
+        window = self._span(window, chunk)
         if extra:
             # (value size, amplitude, norm after the rotation: see qk_norm_rope_store) the
             # general preparation, then attention over rows of the pages' size; the output has
@@ -849,7 +1032,7 @@ class CudaOps:
                        _c_int(view.page_size), _c_int(view.kv.shape[1]),
                        _c_void_p(_ptr(ctx.positions)), _c_void_p(_ptr(out)),
                        _c_void_p(_ptr(partial)), _c_int(tokens), _c_int(heads), _c_int(kv_heads),
-                       _c_int(head_dim), _c_int(splits), _c_float(scale), _c_int(window or 0),
+                       _c_int(head_dim), _c_int(splits), _c_float(scale), _c_int(window),
                        _c_int(1 if write else 0), _c_void_p(_ptr(sinks)),
                        _c_void_p(_ptr(self.error_flag)))
             if partial is not None:
@@ -862,7 +1045,7 @@ class CudaOps:
                                     scale=scale, window=window, ctx=ctx, view=view, sinks=sinks)
 
     def paged_attention(self, q, *, heads, kv_heads, head_dim, scale, window, ctx, view,
-                        sinks=None):
+                        sinks=None, chunk=None):
         """Attention of every token over its request's pages. bfloat16 with a head size that
         is a multiple of 16 up to 128 runs on tensor cores: the split-key decode kernel when
         every request brings one token, else the prefill kernel. Everything else (float32,
@@ -872,6 +1055,9 @@ class CudaOps:
         width = view.block_table.shape[1]
         pages = view.kv.shape[1]
         code = _dtype_code(q.dtype)
+        if chunk:
+            window = self._span(window, chunk)
+        window = int(window or 0)         # (negative: chunks, see _span)
         if sinks is not None:
             # (float32 [heads]: exp(sink) of a query's head stands in its softmax's denominator)
             self._need(sinks, torch.float32, "sinks")
@@ -903,7 +1089,7 @@ class CudaOps:
                 # cut into parts that run side by side, and a merge follows
                 bound = min(ctx.max_context, width * view.page_size)
                 if window:
-                    bound = min(bound, window + ctx.max_portion)
+                    bound = min(bound, abs(window) + ctx.max_portion)
                 splits = 1
                 if self.prefill_key_splits:
                     splits = self.lib.mlxone_attention_tcgen05_splits(
@@ -978,7 +1164,7 @@ class CudaOps:
         """Into how many parts the decode kernel cuts a request's keys: as many blocks as the
         GPU holds at once (one wave), but at least four tiles of 32 keys per part."""
         if window:
-            context_bound = min(context_bound, window + 31)
+            context_bound = min(context_bound, abs(window) + 31)
         tiles = max(-(-context_bound // 32), 1)
         blocks_per_sm = self.lib.mlxone_attention_decode_resident(_c_int(head_dim))
         groups = kv_heads * (-(-(heads // kv_heads) // 8))
