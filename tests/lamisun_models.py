@@ -93,7 +93,7 @@ CONFIGS = {"L1": (L1, 31, 16), "L2": (L2, 32, 8), "L3": (L3, 33, 4), "L4": (L4, 
 
 
 def draw_tensors(config: dict, seed: int) -> dict[str, torch.Tensor]:
-    """Weights for ``config``, by the names and shapes of the engine's weight contract: matrices
+    """Weights for ``config``, by the names and shapes that the engine expects: matrices
     ~ N(0, 1/in), tables N(0, 1), norm weights around 1, convolution weights ~ N(0, 0.5), the
     streams' weights around 1 / their count, the activation's two numbers and the vectors of
     the maps' factor ~ N(0, 0.3)."""
