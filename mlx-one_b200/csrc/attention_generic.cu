@@ -14,7 +14,7 @@
 namespace {
 
 constexpr int WARPS = 4;
-constexpr int MAX_HEAD_DIM = 512;
+constexpr int MAX_HEAD_DIM = 1024;
 constexpr int MAX_ACC = MAX_HEAD_DIM / 32;
 
 template <typename T>

@@ -1,0 +1,423 @@
+// Attention over one latent row per token on tensor cores (bfloat16).
+//
+// A token keeps one row [latent | rotated key part] of R values in single-plane pages; the row
+// is the key of every head and its first `latent` values are every head's value. A query row is
+// a (token, head) pair; the rows of a request's portion are consecutive, token by token. So the
+// heads of a token (and neighbouring tokens) share every key they read, and one block runs
+// 16 * MT query rows against tiles of 64 keys that are copied asynchronously into shared memory
+// (two buffers) while the tile before is in use.
+//
+// A block has 8 warps. For a tile, warp w computes the scores of keys 8w..8w+7 for all rows of
+// the block (bfloat16 products, 32-bit sums) and leaves them, scaled and masked, in shared
+// memory; after a barrier every warp reads the whole 16 MT x 64 scores, keeps the rows' running
+// maximum and sum (32-bit; all warps hold the same numbers), rounds the weights to bfloat16 and
+// multiplies them with its own columns of the latents: warp w owns the 8-column groups w, w + 8,
+// ... of the output (up to 8 groups, so latents up to 512). The output's accumulators are 32-bit.
+//
+// Steps of single tokens cut every request's keys into `splits` runs of tiles that run side by
+// side; each leaves (unnormalised output, maximum, sum) per row in scratch memory and a second
+// kernel merges them.
+//
+// Sizes: R a multiple of 8 up to 576 (padded with zeros to a multiple of 16 in shared memory),
+// latent a multiple of 8 up to 512. Anything else runs the general kernel.
+#include "common.cuh"
+
+namespace {
+
+using bf16 = __nv_bfloat16;
+constexpr int KEYS = 64;           // keys per tile
+constexpr int WARPS = 8;
+constexpr int GROUPS = 8;          // 8-column groups of the output per warp, at most
+constexpr int SCORE_STRIDE = 72;   // floats per row of the scores in shared memory
+constexpr int MAX_ROW = 576;
+constexpr int MAX_LATENT = WARPS * GROUPS * 8;
+
+__device__ __forceinline__ uint32_t shared_address(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void copy16(void* dst, const void* src, bool live) {
+    const int bytes = live ? 16 : 0;          // 0 bytes read: the 16 bytes are filled with zero
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(shared_address(dst)),
+                 "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void copy_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void copy_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(shared_address(p)));
+}
+__device__ __forceinline__ void ldmatrix_x2(uint32_t (&r)[2], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n"
+                 : "=r"(r[0]), "=r"(r[1])
+                 : "r"(shared_address(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(shared_address(p)));
+}
+
+// d += a (16x16, row) * b (16x8, col), bfloat16 in, float accumulate
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                          uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// Copies keys first..first+63 of a request into a tile [64][stride]; rows beyond `last` or
+// without a page are zero.
+__device__ __forceinline__ void load_keys(bf16* tile, int stride, const bf16* pages,
+                                          const int* table, int table_width, int page_size,
+                                          int row_size, int first, int last, int* error_flag) {
+    const int chunks = row_size >> 3;
+    for (int piece = threadIdx.x; piece < KEYS * chunks; piece += WARPS * 32) {
+        const int row = piece / chunks, chunk = piece - row * chunks;
+        const int key = first + row;
+        bool live = key <= last;
+        size_t offset = 0;
+        if (live) {
+            const int block = key / page_size;
+            const int page = block < table_width ? table[block] : -1;
+            live = page >= 0;
+            if (live) offset = ((size_t)page * page_size + (key - block * page_size)) * row_size + chunk * 8;
+            else if (chunk == 0) atomicExch(error_flag, 3);
+        }
+        copy16(tile + row * stride + chunk * 8, pages + offset, live);
+    }
+}
+
+
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ float quad_max(float v) {
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+    return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+}
+__device__ __forceinline__ float quad_sum(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    return v + __shfl_xor_sync(0xffffffffu, v, 2);
+}
+
+// Grid: (blocks of 16 MT rows over the longest portion, requests, splits). Dynamic shared
+// memory: queries [16 MT][stride], keys 2 x [64][stride] (bfloat16, stride = R rounded up to 16,
+// plus 8), scores [16 MT][72] floats. Scores are kept times log2(e), so weights are powers of 2.
+// splits == 1: out [tokens, heads, R] gets its first `latent` values per row. Else partial
+// [splits, total_rows, latent] and stats [splits, total_rows, 2] (maximum, sum) are written.
+template <int MT>
+__global__ void __launch_bounds__(WARPS * 32, 1)
+latent_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pages,
+                        const int* __restrict__ block_table, int table_width, int page_size,
+                        const int* __restrict__ positions, const int* __restrict__ request_start,
+                        bf16* __restrict__ out, float* __restrict__ partial,
+                        float* __restrict__ stats, int total_rows, int heads, int row_size,
+                        int latent, float scale, int splits, int* __restrict__ error_flag) {
+    constexpr int ROWS = 16 * MT;
+    extern __shared__ __align__(16) unsigned char raw[];
+    const int request = blockIdx.y, split = blockIdx.z;
+    const int start = request_start[request];
+    const int rows = (request_start[request + 1] - start) * heads;
+    const int row0 = blockIdx.x * ROWS;
+    if (row0 >= rows) return;
+    const int padded = (row_size + 15) & ~15;
+    const int stride = padded + 8;
+    bf16* q_tile = reinterpret_cast<bf16*>(raw);
+    bf16* k_tiles[2] = {q_tile + ROWS * stride, q_tile + (ROWS + KEYS) * stride};
+    float* scores = reinterpret_cast<float*>(q_tile + (ROWS + 2 * KEYS) * stride);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int history = positions[start];
+    const int live_rows = min(ROWS, rows - row0);
+    const int last_key = history + (row0 + live_rows - 1) / heads;
+    const int tiles = last_key / KEYS + 1;
+    const int per_split = (tiles + splits - 1) / splits;
+    const int tile_first = split * per_split;
+    const int tile_end = min(tiles, tile_first + per_split);
+    const int* table = block_table + (size_t)request * table_width;
+    const size_t first_row = (size_t)start * heads + row0;        // among all rows of the step
+
+    // columns between R and its multiple of 16 are zero in every tile (nothing copies there)
+    if (padded != row_size) {
+        const int extra = padded - row_size;
+        for (int i = threadIdx.x; i < (ROWS + 2 * KEYS) * extra; i += WARPS * 32)
+            q_tile[(i / extra) * stride + row_size + i % extra] = __float2bfloat16_rn(0.f);
+    }
+    {
+        const int chunks = row_size >> 3;
+        for (int piece = threadIdx.x; piece < ROWS * chunks; piece += WARPS * 32) {
+            const int row = piece / chunks, chunk = piece - row * chunks;
+            const bool live = row < live_rows;
+            copy16(q_tile + row * stride + chunk * 8,
+                   q + (live ? (first_row + row) * row_size + chunk * 8 : 0), live);
+        }
+    }
+    if (tile_first < tile_end)
+        load_keys(k_tiles[0], stride, pages, table, table_width, page_size, row_size,
+                  tile_first * KEYS, last_key, error_flag);
+    copy_commit();
+
+    // the positions of this thread's rows (g and g + 8 of every 16)
+    int position[MT][2];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        position[m][0] = history + (row0 + m * 16 + g) / heads;
+        position[m][1] = history + (row0 + m * 16 + g + 8) / heads;
+    }
+    float o[MT][GROUPS][4];
+    float peak[MT][2], total[MT][2];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        peak[m][0] = peak[m][1] = -INFINITY;
+        total[m][0] = total[m][1] = 0.f;
+#pragma unroll
+        for (int j = 0; j < GROUPS; ++j) o[m][j][0] = o[m][j][1] = o[m][j][2] = o[m][j][3] = 0.f;
+    }
+    const float factor = scale * LOG2E;
+
+    for (int tile = tile_first; tile < tile_end; ++tile) {
+        const bf16* keys = k_tiles[(tile - tile_first) & 1];
+        copy_wait<0>();
+        __syncthreads();
+        if (tile + 1 < tile_end)
+            load_keys(k_tiles[(tile + 1 - tile_first) & 1], stride, pages, table, table_width,
+                      page_size, row_size, (tile + 1) * KEYS, last_key, error_flag);
+        copy_commit();
+
+        // ---- scores of this warp's 8 keys for all rows
+        float s[MT][4];
+#pragma unroll
+        for (int m = 0; m < MT; ++m) s[m][0] = s[m][1] = s[m][2] = s[m][3] = 0.f;
+        const bf16* key_rows = keys + (warp * 8 + (lane & 7)) * stride + ((lane >> 3) & 1) * 8;
+        const bf16* query_rows = q_tile + (lane & 15) * stride + (lane >> 4) * 8;
+#pragma unroll 4
+        for (int k0 = 0; k0 < padded; k0 += 16) {
+            uint32_t b[2];
+            ldmatrix_x2(b, key_rows + k0);
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                uint32_t a[4];
+                ldmatrix_x4(a, query_rows + m * 16 * stride + k0);
+                mma_16816(s[m], a, b[0], b[1]);
+            }
+        }
+        const int key0 = tile * KEYS + warp * 8 + 2 * t;
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int limit = position[m][half];
+                float2 v;
+                v.x = key0 <= limit ? s[m][2 * half] * factor : -INFINITY;
+                v.y = key0 + 1 <= limit ? s[m][2 * half + 1] * factor : -INFINITY;
+                *reinterpret_cast<float2*>(scores + (m * 16 + g + 8 * half) * SCORE_STRIDE +
+                                           warp * 8 + 2 * t) = v;
+            }
+        }
+        __syncthreads();
+
+        // ---- every warp: the rows' maximum and sum over the 64 keys, weights in bfloat16
+        uint32_t p[MT][4][4];
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const float* row = scores + (m * 16 + g + 8 * half) * SCORE_STRIDE + 2 * t;
+                float2 x[4][2];
+                float highest = -INFINITY;
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    x[kk][0] = *reinterpret_cast<const float2*>(row + 16 * kk);
+                    x[kk][1] = *reinterpret_cast<const float2*>(row + 16 * kk + 8);
+                    highest = fmaxf(highest, fmaxf(fmaxf(x[kk][0].x, x[kk][0].y),
+                                                   fmaxf(x[kk][1].x, x[kk][1].y)));
+                }
+                highest = fmaxf(quad_max(highest), peak[m][half]);
+                const float base = highest == -INFINITY ? 0.f : highest;
+                const float shrink = exp2f(peak[m][half] - base);
+                peak[m][half] = highest;
+                float sum = 0.f;
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+                    for (int side = 0; side < 2; ++side) {
+                        const float a = exp2f(x[kk][side].x - base), b = exp2f(x[kk][side].y - base);
+                        sum += a + b;
+                        p[m][kk][half + 2 * side] = pack_bf16(a, b);
+                    }
+                }
+                total[m][half] = total[m][half] * shrink + quad_sum(sum);
+#pragma unroll
+                for (int j = 0; j < GROUPS; ++j) {
+                    o[m][j][2 * half] *= shrink;
+                    o[m][j][2 * half + 1] *= shrink;
+                }
+            }
+        }
+
+        // ---- this warp's columns of the output
+#pragma unroll
+        for (int j = 0; j < GROUPS; ++j) {
+            const int column = (warp + WARPS * j) * 8;
+            if (column < latent) {
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t b[4];
+                    ldmatrix_x4_trans(b, keys + (32 * half + lane) * stride + column);
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) {
+                        mma_16816(o[m][j], p[m][2 * half], b[0], b[1]);
+                        mma_16816(o[m][j], p[m][2 * half + 1], b[2], b[3]);
+                    }
+                }
+            }
+        }
+    }
+    copy_wait<0>();
+
+    // ---- results
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int row = m * 16 + g + 8 * half;
+            if (row >= live_rows) continue;
+            const size_t global_row = first_row + row;
+            if (splits == 1) {
+                const float inverse = total[m][half] > 0.f ? 1.f / total[m][half] : 0.f;
+#pragma unroll
+                for (int j = 0; j < GROUPS; ++j) {
+                    const int column = (warp + WARPS * j) * 8 + 2 * t;
+                    if (column < latent)
+                        *reinterpret_cast<uint32_t*>(out + global_row * row_size + column) =
+                            pack_bf16(o[m][j][2 * half] * inverse, o[m][j][2 * half + 1] * inverse);
+                }
+            } else {
+                const size_t at = (size_t)split * total_rows + global_row;
+#pragma unroll
+                for (int j = 0; j < GROUPS; ++j) {
+                    const int column = (warp + WARPS * j) * 8 + 2 * t;
+                    if (column < latent)
+                        *reinterpret_cast<float2*>(partial + at * latent + column) =
+                            make_float2(o[m][j][2 * half], o[m][j][2 * half + 1]);
+                }
+                if (warp == 0 && t == 0) {
+                    stats[2 * at] = peak[m][half];
+                    stats[2 * at + 1] = total[m][half];
+                }
+            }
+        }
+    }
+}
+
+// One block per row: out = sum_s 2^(max_s - max) partial_s / sum_s 2^(max_s - max) sum_s.
+__global__ void __launch_bounds__(128)
+latent_merge_kernel(const float* __restrict__ partial, const float* __restrict__ stats,
+                    bf16* __restrict__ out, int total_rows, int row_size, int latent, int splits) {
+    const int row = blockIdx.x;
+    float highest = -INFINITY;
+    for (int s = 0; s < splits; ++s)
+        highest = fmaxf(highest, stats[2 * ((size_t)s * total_rows + row)]);
+    float sum = 0.f;
+    for (int s = 0; s < splits; ++s) {
+        const size_t at = (size_t)s * total_rows + row;
+        const float peak = stats[2 * at];
+        if (peak != -INFINITY) sum += exp2f(peak - highest) * stats[2 * at + 1];
+    }
+    const float inverse = sum > 0.f ? 1.f / sum : 0.f;
+    for (int column = threadIdx.x; column < latent; column += blockDim.x) {
+        float value = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const size_t at = (size_t)s * total_rows + row;
+            const float peak = stats[2 * at];
+            if (peak != -INFINITY) value += exp2f(peak - highest) * partial[at * latent + column];
+        }
+        out[(size_t)row * row_size + column] = __float2bfloat16_rn(value * inverse);
+    }
+}
+
+template <int MT>
+int launch_latent(const bf16* q, const bf16* pages, const int* block_table, int table_width,
+                  int page_size, const int* positions, const int* request_start, bf16* out,
+                  float* partial, float* stats, int total_rows, int requests, int max_rows,
+                  int heads, int row_size, int latent, float scale, int splits, int* error_flag,
+                  cudaStream_t stream) {
+    constexpr int ROWS = 16 * MT;
+    const int stride = ((row_size + 15) & ~15) + 8;
+    const size_t shared = (size_t)(ROWS + 2 * KEYS) * stride * sizeof(bf16) +
+                          (size_t)ROWS * SCORE_STRIDE * sizeof(float);
+    static bool prepared = false;
+    if (!prepared) {
+        cudaError_t err = cudaFuncSetAttribute(latent_attention_kernel<MT>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)((size_t)(ROWS + 2 * KEYS) * (MAX_ROW + 8) * sizeof(bf16) +
+                                                     (size_t)ROWS * SCORE_STRIDE * sizeof(float)));
+        MLXONE_REQUIRE(err == cudaSuccess, "latent attention: %s", cudaGetErrorString(err));
+        prepared = true;
+    }
+    const dim3 grid((max_rows + ROWS - 1) / ROWS, requests, splits);
+    latent_attention_kernel<MT><<<grid, WARPS * 32, shared, stream>>>(
+        q, pages, block_table, table_width, page_size, positions, request_start, out, partial,
+        stats, total_rows, heads, row_size, latent, scale, splits, error_flag);
+    MLXONE_LAUNCH_CHECK("latent_attention_mma");
+    return 0;
+}
+
+}  // namespace
+
+// 1 if the tensor-core kernel takes rows of `row_size` values with `latent` of them the value.
+MLXONE_API int mlxone_latent_attention_mma_fits(int row_size, int latent) {
+    return row_size % 8 == 0 && row_size <= MAX_ROW && latent % 8 == 0 && latent <= MAX_LATENT &&
+           latent <= row_size && latent > 0;
+}
+
+// q, out [tokens, heads, row_size] bfloat16; pages [pages, page_size, row_size]; max_portion: the
+// most tokens a request brings. scratch (splits > 1 only; every request brings one token):
+// splits * tokens * heads * (latent + 2) floats.
+MLXONE_API int mlxone_latent_attention_mma(const void* q, const void* pages, const int* block_table,
+                                           int table_width, int page_size, const int* positions,
+                                           const int* request_start, void* out, float* scratch,
+                                           int tokens, int requests, int max_portion, int heads,
+                                           int row_size, int latent, float scale, int splits,
+                                           int* error_flag, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    MLXONE_REQUIRE(mlxone_latent_attention_mma_fits(row_size, latent),
+                   "latent attention: rows of %d with %d latent values do not fit", row_size, latent);
+    MLXONE_REQUIRE(requests > 0 && heads > 0 && max_portion > 0 && page_size > 0 && table_width > 0,
+                   "latent attention: bad sizes");
+    MLXONE_REQUIRE(splits >= 1 && (splits == 1 || (max_portion == 1 && scratch != nullptr)),
+                   "latent attention: keys are split only in steps of single tokens");
+    const int total_rows = tokens * heads;
+    float* partial = scratch;
+    float* stats = scratch ? scratch + (size_t)splits * total_rows * latent : nullptr;
+    const long long max_rows = (long long)max_portion * heads;
+    int status;
+    if (max_rows > 16)
+        status = launch_latent<2>((const bf16*)q, (const bf16*)pages, block_table, table_width,
+                                  page_size, positions, request_start, (bf16*)out, partial, stats,
+                                  total_rows, requests, (int)max_rows, heads, row_size, latent,
+                                  scale, splits, error_flag, stream);
+    else
+        status = launch_latent<1>((const bf16*)q, (const bf16*)pages, block_table, table_width,
+                                  page_size, positions, request_start, (bf16*)out, partial, stats,
+                                  total_rows, requests, (int)max_rows, heads, row_size, latent,
+                                  scale, splits, error_flag, stream);
+    if (status) return status;
+    if (splits > 1) {
+        latent_merge_kernel<<<total_rows, 128, 0, stream>>>(partial, stats, (bf16*)out, total_rows,
+                                                            row_size, latent, splits);
+        MLXONE_LAUNCH_CHECK("latent_merge");
+    }
+    return 0;
+}

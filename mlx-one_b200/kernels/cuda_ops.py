@@ -168,8 +168,8 @@ class CudaOps:
     def check_attention_sizes(self, heads: int, kv_heads: int, head_dim: int) -> None:
         if heads % kv_heads:
             raise KernelError(f"{heads} query heads cannot share {kv_heads} key heads")
-        if not 2 <= head_dim <= 512:
-            raise KernelError(f"head size {head_dim} is outside 2..512")
+        if not 2 <= head_dim <= 1024:
+            raise KernelError(f"head size {head_dim} is outside 2..1024")
 
     # ------------------------------------------------------------------ ops
 
@@ -604,6 +604,27 @@ class CudaOps:
         tokens, _, row = queries.shape
         self._need(queries, view.kv.dtype, "queries")
         out = torch.empty((tokens, heads, row), dtype=queries.dtype, device=self.device)
+        if queries.dtype == torch.bfloat16 and \
+                self.lib.mlxone_latent_attention_mma_fits(_c_int(row), _c_int(latent)):
+            # tensor cores: blocks of 16 or 32 (token, head) rows that share the keys they read;
+            # steps of single tokens cut the keys into runs that fill the GPU, merged afterwards
+            splits, scratch = 1, None
+            if ctx.max_portion == 1:
+                blocks = ctx.requests * -(-heads // 16)
+                bound = min(ctx.max_context, view.block_table.shape[1] * view.page_size)
+                splits = max(1, min(self._sm_count // blocks, -(-bound // 64) // 2, 32))
+                if splits > 1:
+                    scratch = torch.empty(splits * tokens * heads * (latent + 2),
+                                          dtype=torch.float32, device=self.device)
+            self._call("mlxone_latent_attention_mma", _c_void_p(_ptr(queries)),
+                       _c_void_p(_ptr(view.kv)), _c_void_p(_ptr(view.block_table)),
+                       _c_int(view.block_table.shape[1]), _c_int(view.page_size),
+                       _c_void_p(_ptr(ctx.positions)), _c_void_p(_ptr(ctx.request_start)),
+                       _c_void_p(_ptr(out)), _c_void_p(_ptr(scratch)), _c_int(tokens),
+                       _c_int(ctx.requests), _c_int(ctx.max_portion), _c_int(heads), _c_int(row),
+                       _c_int(latent), _c_float(scale), _c_int(splits),
+                       _c_void_p(_ptr(self.error_flag)))
+            return out
         self._call("mlxone_attention_generic_planes", _c_void_p(_ptr(queries)),
                    _c_void_p(_ptr(view.kv)), _c_void_p(_ptr(view.block_table)),
                    _c_int(view.block_table.shape[1]), _c_int(view.page_size),

@@ -294,7 +294,8 @@ def test_latent_attention_part(dtype, heads, dim, rot_dim, vdim, kv_rank, hidden
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads, latent_size, rot_dim", [(8, 64, 16), (3, 40, 6), (16, 128, 32)])
+@pytest.mark.parametrize("heads, latent_size, rot_dim", [(8, 64, 16), (3, 40, 6), (16, 128, 32),
+                                                        (20, 200, 24), (16, 512, 64), (5, 72, 8)])
 def test_latent_rows_far_away(ops, dtype, heads, latent_size, rot_dim):
     """One row near the start of 900 matches the last queries by far: their outputs are that
     row's latent, in a prompt's portion and for single tokens of requests side by side."""
@@ -312,14 +313,15 @@ def test_latent_rows_far_away(ops, dtype, heads, latent_size, rot_dim):
     scores = torch.einsum("thd,sd->hts", q.double(), rows.double()) * scale
     weights = plain.softmax_rows(scores, plain.visible(T))
     want = torch.einsum("hts,sd->thd", weights, rows.double()[:, :latent_size])
-    assert want[-1, :, 6].min() > 1.0
+    assert want[-1, :, 6].min() > 0.5                    # the far row is what the output is
     table, pool = page_tables((T,), page, generator)
     kv = torch.full((1, pool, 1, page, row), 100.0).to(dtype)
     for t in range(T):
         kv[0, table[0, t // page], 0, t % page] = rows[t]
     need = PagedKeyValues(1, row, planes=1)
     tolerance = 1e-4 if dtype == torch.float32 else 0.04
-    for portions, histories in (([40], [T - 40]), ([1] * 3, [T - 1, T - 2, T - 3]),
+    for portions, histories in (([40], [T - 40]), ([T], [0]), ([1] * 3, [T - 1, T - 2, T - 3]),
+                                ([333, 1, 70], [T - 333, 63, 58]),
                                 ([1] * 30, [T - 1 - i for i in range(30)]), ([2, 1], [T - 2, 4])):
         ctx = context(portions, histories)
         positions = ctx.positions.tolist()
@@ -491,7 +493,9 @@ def test_the_stream_after_every_layer(folders, models):
         models[name].logits(tokens, states)
         assert len(seen) == len(states) == len(config["layers"]) + 1
         for place, (got, want) in enumerate(zip(seen, states)):
-            assert (got.cpu().double() - want).abs().max() < 2e-4, f"{name} after call {place - 1}"
+            # (a step's rows may be padded to a shape that is replayed)
+            got = got[:len(tokens)].cpu().double()
+            assert (got - want).abs().max() < 2e-4, f"{name} after call {place - 1}"
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
