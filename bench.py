@@ -17,6 +17,8 @@ Two more workloads, each printing one JSON line of its own (the default line is 
 
     python bench.py --case batching     continuous batching of 128 requests at the LFM2-700M shape
     python bench.py --case long         4 x 32,768-token prompts at the LFM2-350M shape, then decoding
+    python bench.py --case lamisun      Lamisun beside LFM2 at equal width, depth and vocabulary:
+                                        decode and prefill tokens/s, and the new kernels alone
     python bench.py --case farorax      Farorax beside Galarax at equal width, depth and vocabulary:
                                         decode and prefill tokens/s, and the new kernels alone
     python bench.py --case galarax      Galarax beside LFM2 at equal width, depth and vocabulary:
@@ -213,7 +215,8 @@ def model_flops(spec, tokens):
             used[layer.prefix + part.prefix] = part["top"] / part["experts"]
     for name, tensor in expected_tensors(spec).items():
         if len(tensor.shape) == 2 and name != spec.embedding and name != spec.head \
-                and not name.endswith(("conv.conv", ".conv", ".router")) and name not in spec.vectors:
+                and not name.endswith(("conv.conv", ".conv", ".router", ".canon1", ".canon2")) \
+                and name != "bigram" and name not in spec.vectors:
             share = 1.0
             found = re.match(r"(.*\.)e\d+\.(gate|up|down)$", name)
             if found and found.group(1) in used:
@@ -229,6 +232,15 @@ def model_flops(spec, tokens):
                 window = part.get("window") or tokens
                 seen = sum(min(i + 1, window) for i in range(tokens))
                 flops += 4 * width * seen                       # causal (windowed) QK^T and PV
+            elif part.kind == "latent_attention":
+                # every head's query against the one row per token, and the weights' average of
+                # the latents
+                row = part["latent"] + part["rot_dim"]
+                flops += 2 * part["heads"] * (row + part["latent"]) * tokens * (tokens + 1) // 2
+            elif part.kind == "differential_attention":
+                chunk = part.get("chunk") or tokens
+                seen = sum(i % chunk + 1 for i in range(tokens))
+                flops += 4 * part["heads"] * (part["head_dim"] + part["value_dim"]) * seen
             elif part.kind == "lightning":
                 # 32-bit multiply-adds of the recurrence (not tensor-core work, but work)
                 flops += 4 * tokens * part["heads"] * part["key_dim"] * part["value_dim"]
@@ -1114,6 +1126,283 @@ def case_farorax(args) -> int:
     return 0
 
 
+# --------------------------------------------------------------------------- Lamisun beside LFM2
+
+
+def lamisun_shape(width: int, layers: int, vocab: int = 65536) -> dict:
+    """A Lamisun of the sizes that a model of this width has: layers in turn with attention over
+    latent rows (heads of 64 unrotated + a rotated part shared by the heads, a latent of a quarter
+    of the width) and differential attention (two maps of 64 per head, one key head per four
+    query heads, chunks of 1024 positions, as many score maps as LFM2 has heads), feed-forwards
+    four times the width, four taps, a pair table of 65,536 buckets."""
+    rot_dim, latent = (32, 256) if width <= 1024 else (64, 512)
+    first = {"heads": width // 64, "dim": 64, "rot_dim": rot_dim, "vdim": 64, "kv_rank": latent,
+             "scale": (64 + rot_dim) ** -0.5, "rot": {"base": 10000.0, "dims": rot_dim}}
+    second = {"heads": width // 128, "kv_heads": width // 512, "dim": 64, "vdim": 64,
+              "scale": 0.125, "diff": 0.2, "mask": {"size": 1024}}
+    dense = {"kind": "dense", "ff": 4 * width}
+    entries = [{"type": "attention", "mixer": second, "mlp": dense} if index % 2 else
+               {"type": "latent_attention", "mixer": first, "mlp": dense} for index in range(layers)]
+    return {"architecture": "Lamisun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0, "bigram": {"buckets": 65536, "mul_prev": 1000003,
+                                                   "mul_cur": 31}},
+            "canon": {"taps": 4}, "layers": entries}
+
+
+def lamisun_kernels(width, batch, peak):
+    """The kernels that Lamisun adds, alone, beside the like kernels of LFM2, for a decode step
+    of ``batch`` tokens over 2,048 earlier ones and a prompt of PREFILL_TOKENS tokens:
+    algorithmic bytes (or flops) / time against the measured peaks. Arguments rotate over copies
+    that together exceed L2."""
+    import torch
+
+    from mlx_one_b200.kernels import default_ops
+    from mlx_one_b200.parts import (FixedState, PagedKeyValues, PagedView, StateView,
+                                    StepContext)
+
+    ops, device = default_ops("cuda:0"), "cuda:0"
+    ints = lambda values: torch.tensor(values, dtype=torch.int32, device=device)
+    bf16 = lambda *shape: torch.randn(*shape, device=device).bfloat16()
+
+    def ctx_of(portions, histories):
+        positions, owner, starts = [], [], [0]
+        for r, (n, before) in enumerate(zip(portions, histories)):
+            positions += list(range(before, before + n))
+            owner += [r] * n
+            starts.append(starts[-1] + n)
+        return StepContext(tokens=len(positions), requests=len(portions),
+                           token_ids=ints([0] * len(positions)), positions=ints(positions),
+                           token_request=ints(owner), request_start=ints(starts),
+                           history=ints(histories), max_portion=max(portions),
+                           max_context=max(p + h for p, h in zip(portions, histories)))
+
+    def entry(seconds, moved=None, flops=None):
+        out = {"us": round(seconds * 1e6, 2)}
+        if moved is not None:
+            out["gbs"] = round(moved / seconds / 1e9, 1)
+            out["hbm_frac"] = round(moved / seconds / 1e9 / peak["hbm_gbs"], 4)
+        if flops is not None:
+            out["tflops"] = round(flops / seconds / 1e12, 2)
+            out["tensor_frac"] = round(flops / seconds / 1e12 / peak["bf16_tflops"], 4)
+        return out
+
+    shape = lamisun_shape(width, 2)
+    first, second = shape["layers"][0]["mixer"], shape["layers"][1]["mixer"]
+    taps, vocab, buckets = 4, 65536, 65536
+    out = {}
+    for label, portions, histories in (("decode", [1] * batch, [2048] * batch),
+                                       ("prefill", [PREFILL_TOKENS], [0])):
+        ctx = ctx_of(portions, histories)
+        tokens, requests = ctx.tokens, ctx.requests
+        copies = 8 if label == "prefill" else 4
+        slots = ints(list(range(requests)))
+        # ---- the embedding with the pair table, beside LFM2's plain rows
+        table, pairs = bf16(vocab, width), bf16(buckets + 1, width)
+        ids = [torch.randint(0, vocab, (tokens,), device=device, dtype=torch.int32)
+               for _ in range(copies)]
+        last = StateView(torch.ones(requests, 1, dtype=torch.int32, device=device), slots,
+                         FixedState((1,), "int32"))
+        stream = [torch.zeros(tokens, width, device=device) for _ in range(copies)]
+        seconds = graph_seconds(lambda i: ops.embedding_pairs(
+            ids[i], table, 1.0, pairs, rule=(buckets, 1000003, 31), ctx=ctx, view=last,
+            out=stream[i]), copies, 2 * copies)
+        out[f"{label}_embedding_pairs"] = entry(seconds, tokens * width * (2 + 2 + 4))
+        seconds = graph_seconds(lambda i: ops.embedding(ids[i], table), copies, 2 * copies)
+        out[f"{label}_embedding_lfm2"] = entry(seconds, tokens * width * (2 + 2))
+        del table, pairs
+        # ---- what a sublayer reads: the stream plus its convolution over time, beside LFM2's
+        # norm of the stream (both read 32-bit rows and write the compute dtype)
+        kept = torch.zeros(requests, 2, taps - 1, width, device=device)
+        inputs = StateView(kept, slots, FixedState((2, taps - 1, width), "float32"))
+        kernel = torch.randn(width, taps, device=device) * 0.1
+        seconds = graph_seconds(lambda i: ops.stream_conv(
+            stream[i], kernel, taps=taps, ctx=ctx, view=inputs, sublayer=0, write=True,
+            dtype=torch.bfloat16), copies, 2 * copies)
+        out[f"{label}_stream_conv"] = entry(
+            seconds, tokens * width * (4 + 2) + 2 * requests * (taps - 1) * width * 4)
+        weight = torch.ones(width, device=device)
+        seconds = graph_seconds(lambda i: ops.add_rmsnorm(stream[i], None, weight, 1e-6,
+                                                          torch.bfloat16), copies, 2 * copies)
+        out[f"{label}_rmsnorm_lfm2"] = entry(seconds, tokens * width * (4 + 2))
+        # ---- a part's output, normed, into the stream, beside LFM2's add + norm
+        delta = [bf16(tokens, width) for _ in range(copies)]
+        seconds = graph_seconds(lambda i: ops.normed_mean_add(stream[i], [delta[i]], [weight],
+                                                              1e-6), copies, 2 * copies)
+        out[f"{label}_add_normed"] = entry(seconds, tokens * width * (4 + 4 + 2))
+        seconds = graph_seconds(lambda i: ops.add_rmsnorm(stream[i], delta[i], weight, 1e-6,
+                                                          torch.bfloat16), copies, 2 * copies)
+        out[f"{label}_add_rmsnorm_lfm2"] = entry(seconds, tokens * width * (4 + 4 + 2 + 2))
+        # ---- the weighted sum of the streams kept so far (after the eighth layer: nine of them)
+        count = 9
+        many = [torch.zeros(count + 1, tokens, width, device=device) for _ in range(2)]
+        average = torch.full((count,), 1.0 / count, device=device)
+        seconds = graph_seconds(lambda i: ops.stream_average(many[i], average, count,
+                                                             many[i][count]), 2, 4)
+        out[f"{label}_stream_average_9"] = entry(seconds, tokens * width * 4 * (count + 1))
+        del many, stream, delta
+        # ---- attention over latent rows: the preparation (latent norm, rotation, page write)
+        # beside LFM2's (head norms, rotation, page write), then attention itself
+        heads, nope, rot, latent = first["heads"], first["dim"], first["rot_dim"], first["kv_rank"]
+        row = latent + rot
+        span = histories[0] + portions[0]
+        pages = -(-span // PAGE_SIZE)
+        blocks = ints([[r * pages + b for b in range(pages)] for r in range(requests)])
+        rows = (torch.randn(1, requests * pages + 1, 1, PAGE_SIZE, row, device=device) * 0.3).bfloat16()
+        latent_view = PagedView(rows, blocks, PAGE_SIZE, PagedKeyValues(1, row, planes=1))
+        wide = heads * (nope + rot) + row + heads * first["vdim"]
+        projected = [bf16(tokens, wide) for _ in range(copies)]
+        queries = [bf16(tokens, heads, row) * 0.3 for _ in range(copies)]
+        inv_freq = torch.rand(rot // 2, device=device)
+        norm_weight = torch.ones(latent, device=device)
+        seconds = graph_seconds(lambda i: ops.latent_prepare(
+            projected[i], queries[i], heads=heads, head_dim=nope, rot_dim=rot, latent=latent,
+            norm_weight=norm_weight, eps=1e-6, rotary=(inv_freq, rot), neighbours=True, ctx=ctx,
+            view=latent_view, write=True), copies, 2 * copies)
+        out[f"{label}_latent_prepare"] = entry(
+            seconds, tokens * ((heads * rot + row) * 2 + (heads * rot + row) * 2))
+        lfm_heads, lfm_kv, head = width // 64, width // 256, 64
+        kv = (torch.randn(2, requests * pages + 1, lfm_kv, PAGE_SIZE, head, device=device) * 0.3).bfloat16()
+        view = PagedView(kv, blocks, PAGE_SIZE, PagedKeyValues(lfm_kv, head, None))
+        qkv = [bf16(tokens, (lfm_heads + 2 * lfm_kv) * head) for _ in range(copies)]
+        ones, inv_full = torch.ones(head, device=device), torch.rand(head // 2, device=device)
+        seconds = graph_seconds(lambda i: ops.qk_norm_rope_store(
+            qkv[i], heads=lfm_heads, kv_heads=lfm_kv, head_dim=head, q_weight=ones, k_weight=ones,
+            eps=1e-6, rotary=(inv_full, head), ctx=ctx, view=view, write=True), copies, 2 * copies)
+        out[f"{label}_qk_prep_lfm2"] = entry(seconds, tokens * (lfm_heads + 2 * lfm_kv) * head * 2 * 2)
+        seen = sum(h + i + 1 for n, h in zip(portions, histories) for i in range(n))
+        seconds = graph_seconds(lambda i: ops.latent_attention(
+            queries[i], heads=heads, latent=latent, scale=first["scale"], ctx=ctx,
+            view=latent_view), copies, 2 * copies)
+        out[f"{label}_latent_attention"] = entry(
+            seconds, requests * span * row * 2 + tokens * heads * row * 2 * 2,
+            2.0 * heads * (row + latent) * seen)
+        q = [bf16(tokens, lfm_heads, head) for _ in range(copies)]
+        seconds = graph_seconds(lambda i: ops.paged_attention(
+            q[i], heads=lfm_heads, kv_heads=lfm_kv, head_dim=head, scale=0.125, window=None,
+            ctx=ctx, view=view), copies, 2 * copies)
+        out[f"{label}_attention_lfm2"] = entry(
+            seconds, requests * span * lfm_kv * head * 2 * 2 + tokens * lfm_heads * head * 2 * 2,
+            4.0 * lfm_heads * head * seen)
+        # ---- the products head by head around the attention (a library's batched product)
+        up_k = bf16(heads, latent, nope) * 0.05
+        up_v = bf16(heads, first["vdim"], latent) * 0.05
+        seconds = graph_seconds(lambda i: ops.linear_heads(
+            projected[i][:, :heads * (nope + rot)].view(tokens, heads, -1)[:, :, :nope], up_k,
+            out=queries[i][:, :, :latent]), copies, 2 * copies)
+        out[f"{label}_heads_up_k"] = entry(seconds, None, 2.0 * tokens * heads * latent * nope)
+        out[f"{label}_heads_up_k"]["weights_gbs"] = round(up_k.numel() * 2 / seconds / 1e9, 1)
+        seconds = graph_seconds(lambda i: ops.linear_heads(queries[i][:, :, :latent], up_v),
+                                copies, 2 * copies)
+        out[f"{label}_heads_up_v"] = entry(seconds, None, 2.0 * tokens * heads * latent * first["vdim"])
+        out[f"{label}_heads_up_v"]["weights_gbs"] = round(up_v.numel() * 2 / seconds / 1e9, 1)
+        # ---- the sigmoid gate on the heads' outputs
+        inner = heads * first["vdim"]
+        values = [bf16(tokens, inner) for _ in range(copies)]
+        seconds = graph_seconds(lambda i: ops.sigmoid_gate(values[i], projected[i][:, wide - inner:]),
+                                copies, 2 * copies)
+        out[f"{label}_sigmoid_gate"] = entry(seconds, tokens * inner * 2 * 3)
+        del rows, projected, queries, q, values
+        # ---- differential attention: two maps per head within chunks, beside LFM2's heads over
+        # every earlier key (from the fused projection to the mixed heads)
+        dh, dkv, dim, chunk = second["heads"], second["kv_heads"], second["dim"], second["mask"]["size"]
+        both = (torch.randn(2, requests * pages + 1, 2 * dkv, PAGE_SIZE, dim, device=device) * 0.3).bfloat16()
+        maps_view = PagedView(both, blocks, PAGE_SIZE, PagedKeyValues(2 * dkv, dim, chunk=chunk))
+        two = [bf16(tokens, (2 * dh + 4 * dkv) * dim) for _ in range(copies)]
+        dim_ones = torch.ones(dim, device=device)
+        seen_chunk = sum((h + i) % chunk + 1 for n, h in zip(portions, histories) for i in range(n))
+        read = lambda kv_heads, size, keys: requests * keys * kv_heads * size * 2 * 2
+        seconds = graph_seconds(lambda i: ops.qkv_attention(
+            two[i], heads=2 * dh, kv_heads=2 * dkv, head_dim=dim, q_weight=dim_ones,
+            k_weight=dim_ones, eps=1e-6, rotary=None, scale=0.125, window=None, chunk=chunk,
+            ctx=ctx, view=maps_view, write=True), copies, 2 * copies)
+        keys_read = min(span, (histories[0] % chunk) + portions[0]) if label == "decode" else span
+        out[f"{label}_differential_maps"] = entry(
+            seconds, read(2 * dkv, dim, keys_read) + tokens * (4 * dh + 4 * dkv) * dim * 2,
+            4.0 * 2 * dh * dim * seen_chunk)
+        seconds = graph_seconds(lambda i: ops.qkv_attention(
+            qkv[i], heads=lfm_heads, kv_heads=lfm_kv, head_dim=head, q_weight=ones, k_weight=ones,
+            eps=1e-6, rotary=(inv_full, head), scale=0.125, window=None, ctx=ctx, view=view,
+            write=True), copies, 2 * copies)
+        out[f"{label}_qkv_attention_lfm2"] = entry(
+            seconds, read(lfm_kv, head, span) + tokens * (2 * lfm_heads + 2 * lfm_kv) * head * 2,
+            4.0 * lfm_heads * head * seen)
+        maps = [bf16(tokens, 2 * dh * dim) for _ in range(copies)]
+        seconds = graph_seconds(lambda i: ops.differential_combine(
+            maps[i], heads=dh, row_dim=dim, value_dim=dim, mix=0.3, eps=1e-6, factor=0.8),
+            copies, 2 * copies)
+        out[f"{label}_differential_combine"] = entry(seconds, tokens * dh * dim * 2 * 3)
+        del both, two, maps, kv, qkv
+        # ---- the feed-forward's first product with xielu, beside the gated one of LFM2
+        ff = 4 * width
+        wcopies = max(2, min(12, int(300e6 // (ff * width * 2))))
+        up = [bf16(ff, width) * 0.02 for _ in range(wcopies)]
+        gate_up = [bf16(2 * ff, width) * 0.02 for _ in range(wcopies)]
+        x = bf16(tokens, width)
+        for name, fn, rows_w in (
+                ("up_xielu", lambda i: ops.linear_act(x, up[i], "xielu", (0.8, 0.8)), ff),
+                ("up_swiglu_lfm2", lambda i: ops.linear_swiglu(x, gate_up[i]), 2 * ff)):
+            seconds = graph_seconds(fn, wcopies, wcopies)
+            out[f"{label}_{name}"] = entry(
+                seconds, rows_w * width * 2 if label == "decode" else None,
+                2.0 * tokens * rows_w * width if label == "prefill" else None)
+        del up, gate_up
+        torch.cuda.empty_cache()
+    return out
+
+
+def case_lamisun(args) -> int:
+    """Lamisun beside LFM2 (the closest of the engine's models: softmax attention with normed
+    queries and keys over paged keys, a convolution over time, a dense feed-forward) at equal
+    width, depth and vocabulary, random weights: decode tokens/s at ``--batch`` and ``--context``
+    (device-timed graph replays of the engine's step), prefill tokens/s of one 2,048-token
+    prompt, each against its bound, and the new kernels alone."""
+    import gc
+
+    import torch
+
+    peak = peaks()
+    warmup, steps = max(args.warmup, 3), min(args.steps, 128)
+    context = args.context or 2048
+    layers = min(args.layers, 8)
+    results = {}
+    for width, twin in ((1024, LFM2_350M), (2048, LFM2_1_2B)):
+        lfm2 = dict(twin)
+        lfm2["layer_types"] = lfm2["layer_types"][:layers]
+        lfm2["num_hidden_layers"] = layers
+        for label, data in ((f"lamisun_w{width}", lamisun_shape(width, layers)),
+                            (f"lfm2_w{width}", lfm2)):
+            engine = engine_of(data, args.batch, context, warmup + steps, f"random-{label}")
+            model, spec = engine.model, engine.model.spec
+            weight_bytes = model.weight_bytes()
+            kv_per_token = engine.cache_bytes_per_token()
+            state_bytes = sum(g.storage[:, 0].numel() * g.storage.element_size()
+                              for g in engine.cache.states)
+            seconds, _, mean_context, launches = time_decode(engine, args.batch, context, warmup,
+                                                             steps, seed=3)
+            step_bytes = weight_bytes + args.batch * (mean_context * kv_per_token + 2 * state_bytes)
+            prefill_seconds = time_prefill(engine, PREFILL_TOKENS, 2, 3, seed=5)
+            flops = model_flops(spec, PREFILL_TOKENS)
+            results[label] = {
+                "layers": layers, "weight_mb": round(weight_bytes / 1e6, 1),
+                "state_mb_per_request": round(state_bytes / 1e6, 2),
+                "decode_tokens_per_s": round(args.batch * steps / seconds, 1),
+                "decode_ms_per_step": round(seconds / steps * 1e3, 4),
+                "decode_hbm_frac": round(step_bytes / (seconds / steps) / 1e9 / peak["hbm_gbs"], 4),
+                "launches_per_step": launches,
+                "prefill_tokens_per_s": round(PREFILL_TOKENS / prefill_seconds, 1),
+                "prefill_ms": round(prefill_seconds * 1e3, 3),
+                "prefill_tensor_frac": round(flops / prefill_seconds / (peak["bf16_tflops"] * 1e12), 4)}
+            del engine, model
+            gc.collect()
+            torch.cuda.empty_cache()
+        results[f"kernels_w{width}"] = lamisun_kernels(width, args.batch, peak)
+    print(json.dumps({"case": "lamisun", "batch": args.batch, "context": context, "steps": steps,
+                      "warmup": warmup, "dtype": "bf16", "peaks": peak["source"],
+                      "data": "synthetic: random weights, seeded uniform-random token ids",
+                      "results": results}))
+    return 0
+
+
 def decode_step_case(batch: int, context: int) -> int:
     """A few eager decode steps of the whole model at the benchmark's sizes, for a list of the
     step's launches (`ncu --metrics gpu__time_duration.sum`): the prompts are fed first, the last
@@ -1474,7 +1763,7 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--context", type=int, default=None,
                         help="context length (default 4096; --case long: prompt tokens, 32768)")
-    parser.add_argument("--case", default="decode", choices=["decode", "batching", "long", "galarax", "farorax"],
+    parser.add_argument("--case", default="decode", choices=["decode", "batching", "long", "galarax", "farorax", "lamisun"],
                         help="decode: the default line; batching: 128 requests batched "
                              "continuously (LFM2-700M shape); long: 4 x 32,768 tokens "
                              "(LFM2-350M shape)")
@@ -1507,6 +1796,8 @@ def main() -> int:
         return case_galarax(args)
     if args.case == "farorax":
         return case_farorax(args)
+    if args.case == "lamisun":
+        return case_lamisun(args)
     args.context = args.context or 4096
     if args.kernel:
         return kernel_case(args.kernel, args.batch, args.context)

@@ -63,6 +63,8 @@ struct ConvUpdate {
     int write_state = 0;
     // (rides along for the gated epilogue: the activation of the gate, silu unless said otherwise)
     int gate = MLXONE_ACT_SILU;
+    // (and for ACTIVATE: the two numbers of an activation that has some, as xielu)
+    float act_a = 0.f, act_b = 0.f;
 };
 
 __device__ __forceinline__ uint32_t shared_address(const void* p) {
@@ -624,7 +626,8 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
             } else if (EPILOGUE == ACTIVATE) {
                 // (the product is rounded as if it had been stored, then activated)
                 reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] = __float2bfloat16_rn(
-                    mlxone_activate(__bfloat162float(__float2bfloat16_rn(value)), up_offset));
+                    mlxone_activate(__bfloat162float(__float2bfloat16_rn(value)), up_offset,
+                                    conv.act_a, conv.act_b));
             } else if (EPILOGUE == ADD_RESIDUAL) {
                 // added where the value lives (one addition per address, so the result is the
                 // same): the thread does not wait for the old value to come and go
@@ -745,6 +748,32 @@ MLXONE_API int mlxone_gemm_skinny_scaled_add(const void* a, int lda, const void*
     memcpy(&bits, &scale, sizeof(bits));
     const cudaError_t err = launch_for_rows<ADD_RESIDUAL>(a, lda, w, bias, out, ldo, m, n, k, bits,
                                                           stream);
+    if (err != cudaSuccess) {
+        mlxone_set_error("gemm_skinny: launch failed: %s", cudaGetErrorString(err));
+        return 2;
+    }
+    MLXONE_LAUNCH_CHECK("gemm_skinny");
+    return 0;
+}
+
+// out bf16 [m, n] = activation(a w^T + bias), for an activation with two numbers of its own.
+MLXONE_API int mlxone_gemm_skinny_shaped(const void* a, int lda, const void* w, const float* bias,
+                                         void* out, int ldo, int m, int n, int k, int activation,
+                                         float act_a, float act_b, cudaStream_t stream) {
+    if (m == 0 || n == 0) return 0;
+    MLXONE_REQUIRE(m > 0 && m <= 32, "gemm_skinny: %d rows, at most 32", m);
+    MLXONE_REQUIRE(n > 0 && k > 0 && k % 8 == 0 && lda % 8 == 0,
+                   "gemm_skinny: K (%d) and the row stride of a (%d) must be multiples of 8", k, lda);
+    MLXONE_REQUIRE((reinterpret_cast<uintptr_t>(a) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(w) & 15) == 0,
+                   "gemm_skinny: operands must be 16-byte aligned");
+    MLXONE_REQUIRE(activation >= 0 && activation <= MLXONE_ACT_XIELU,
+                   "gemm_skinny: unknown activation %d", activation);
+    ConvUpdate shaped;
+    shaped.act_a = act_a;
+    shaped.act_b = act_b;
+    const cudaError_t err = launch_for_rows<ACTIVATE>(a, lda, w, bias, out, ldo, m, n, k, activation,
+                                                      stream, NormInput(), shaped);
     if (err != cudaSuccess) {
         mlxone_set_error("gemm_skinny: launch failed: %s", cudaGetErrorString(err));
         return 2;

@@ -457,12 +457,21 @@ class CudaOps:
     def linear_act(self, a, w, kind, params=None):
         """act(a @ w^T): for few rows the activation is the skinny product's epilogue (also with
         the norm of its input applied while loading); else the product, then the activation
-        kernel. An activation with numbers of its own (``params``) is always the latter."""
+        kernel. ``params``: the two numbers of an activation that has some (xielu)."""
         if kind not in self.ACTIVATIONS:
             raise KernelError(f"unknown activation {kind!r}")
         if params is not None:
             if isinstance(a, NormedInput):
                 a = a.materialize()
+            self._check_product(a, w)
+            if self._skinny(a, w, fused=True):
+                out = torch.empty((a.shape[0], w.shape[0]), dtype=a.dtype, device=self.device)
+                self._call("mlxone_gemm_skinny_shaped", _c_void_p(_ptr(a)), _c_int(a.stride(0)),
+                           _c_void_p(_ptr(w)), _c_void_p(None), _c_void_p(_ptr(out)),
+                           _c_int(w.shape[0]), _c_int(a.shape[0]), _c_int(w.shape[0]),
+                           _c_int(a.shape[1]), _c_int(self.ACTIVATIONS[kind]),
+                           _c_float(params[0]), _c_float(params[1]))
+                return out
             return self.activation(self.linear(a, w), kind, params)
         epilogue = self._ACTIVATE + self.ACTIVATIONS[kind]
         if isinstance(a, NormedInput):
