@@ -124,14 +124,15 @@ latent_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
                         const int* __restrict__ positions, const int* __restrict__ request_start,
                         bf16* __restrict__ out, float* __restrict__ partial,
                         float* __restrict__ stats, int total_rows, int heads, int row_size,
-                        int latent, float scale, int splits, int* __restrict__ error_flag) {
+                        int latent, float scale, int splits, int row_limit,
+                        int* __restrict__ error_flag) {
     constexpr int ROWS = 16 * MT;
     extern __shared__ __align__(16) unsigned char raw[];
     const int request = blockIdx.y, split = blockIdx.z;
     const int start = request_start[request];
     const int rows = (request_start[request + 1] - start) * heads;
     const int row0 = blockIdx.x * ROWS;
-    if (row0 >= rows) return;
+    if (row0 >= rows || (row_limit > 0 && rows >= row_limit)) return;   // (the long kernel's)
     const int padded = (row_size + 15) & ~15;
     const int stride = padded + 8;
     bf16* q_tile = reinterpret_cast<bf16*>(raw);
@@ -321,6 +322,202 @@ latent_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
     }
 }
 
+// ---- portions of many rows
+// A warp owns 16 query rows for the whole pass over the keys, as flash attention does: their
+// scores of a tile of 64 keys stay in registers (8 accumulators of 16 x 8), the rows' maximum
+// and sum are kept by the four lanes that hold a row, the weights go from the scores'
+// accumulators straight into the operand of the second product, and the warp accumulates its
+// rows' output columns in registers. No scores pass through shared memory and the block meets
+// only once per tile, where the key buffers change hands.
+//
+// An output of 16 x 256 fills 128 registers, so wider latents are split between C = 2 warps
+// that own the same 16 rows and one half of the columns each; both compute the rows' scores.
+// A block has 8 warps: 128 / C rows. Shared memory: queries [128 / C][stride], keys
+// 2 x [64][stride]. Requests with fewer than LONG_ROWS rows in the step are left to the kernel
+// above (they would keep one warp busy and seven idle).
+constexpr int LONG_TILES = 32;     // 8-column groups of the output per warp
+constexpr int LONG_ROWS = 64;      // a request's rows from which this kernel takes it
+constexpr size_t MAX_SHARED = 227 * 1024;   // what a block may ask for
+
+template <int C>
+__global__ void __launch_bounds__(WARPS * 32, 1)
+latent_attention_long_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pages,
+                             const int* __restrict__ block_table, int table_width, int page_size,
+                             const int* __restrict__ positions,
+                             const int* __restrict__ request_start, bf16* __restrict__ out,
+                             int heads, int row_size, int latent, float scale,
+                             int* __restrict__ error_flag) {
+    constexpr int ROWS = 16 * (WARPS / C);
+    extern __shared__ __align__(16) unsigned char raw[];
+    const int request = blockIdx.y;
+    const int start = request_start[request];
+    const int rows = (request_start[request + 1] - start) * heads;
+    // (the blocks with the most keys first)
+    const int row0 = (gridDim.x - 1 - blockIdx.x) * ROWS;
+    if (row0 >= rows || rows < LONG_ROWS) return;
+    const int padded = (row_size + 15) & ~15;
+    const int stride = padded + 8;
+    bf16* q_tile = reinterpret_cast<bf16*>(raw);
+    bf16* k_tiles[2] = {q_tile + ROWS * stride, q_tile + (ROWS + KEYS) * stride};
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int group = warp / C, side = warp % C;          // rows 16 group .., columns 256 side ..
+    const int history = positions[start];
+    const int live_rows = min(ROWS, rows - row0);
+    const int last_key = history + (row0 + live_rows - 1) / heads;
+    const int tiles = last_key / KEYS + 1;
+    const int* table = block_table + (size_t)request * table_width;
+    const size_t first_row = (size_t)start * heads + row0;
+
+    if (padded != row_size) {
+        const int extra = padded - row_size;
+        for (int i = threadIdx.x; i < (ROWS + 2 * KEYS) * extra; i += WARPS * 32)
+            q_tile[(i / extra) * stride + row_size + i % extra] = __float2bfloat16_rn(0.f);
+    }
+    {
+        const int chunks = row_size >> 3;
+        for (int piece = threadIdx.x; piece < ROWS * chunks; piece += WARPS * 32) {
+            const int row = piece / chunks, chunk = piece - row * chunks;
+            const bool live = row < live_rows;
+            copy16(q_tile + row * stride + chunk * 8,
+                   q + (live ? (first_row + row) * row_size + chunk * 8 : 0), live);
+        }
+    }
+    load_keys(k_tiles[0], stride, pages, table, table_width, page_size, row_size, 0, last_key,
+              error_flag);
+    copy_commit();
+
+    int position[2];
+    position[0] = history + (row0 + group * 16 + g) / heads;
+    position[1] = history + (row0 + group * 16 + g + 8) / heads;
+    // (a warp whose rows all lie beyond the portion still meets the others at the barriers)
+    const int warp_last = history + min(row0 + group * 16 + 15, rows - 1) / heads;
+    const bool idle = group * 16 >= live_rows;
+    float o[LONG_TILES][4];
+#pragma unroll
+    for (int j = 0; j < LONG_TILES; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+    float peak[2] = {-INFINITY, -INFINITY}, total[2] = {0.f, 0.f};
+    const float factor = scale * LOG2E;
+    const bf16* query_rows = q_tile + (group * 16 + (lane & 15)) * stride + (lane >> 4) * 8;
+
+    for (int tile = 0; tile < tiles; ++tile) {
+        const bf16* keys = k_tiles[tile & 1];
+        copy_wait<0>();
+        __syncthreads();
+        if (tile + 1 < tiles)
+            load_keys(k_tiles[(tile + 1) & 1], stride, pages, table, table_width, page_size,
+                      row_size, (tile + 1) * KEYS, last_key, error_flag);
+        copy_commit();
+        if (idle || tile * KEYS > warp_last) continue;        // no key of the tile is visible
+
+        // ---- scores of the warp's 16 rows against the tile's 64 keys
+        float s[8][4];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+        const bf16* key_rows = keys + ((lane & 7) + ((lane >> 4) << 3)) * stride +
+                               ((lane >> 3) & 1) * 8;
+#pragma unroll 2
+        for (int k0 = 0; k0 < padded; k0 += 16) {
+            uint32_t a[4];
+            ldmatrix_x4(a, query_rows + k0);
+#pragma unroll
+            for (int pair = 0; pair < 4; ++pair) {
+                uint32_t b[4];
+                ldmatrix_x4(b, key_rows + pair * 16 * stride + k0);
+                mma_16816(s[2 * pair], a, b[0], b[1]);
+                mma_16816(s[2 * pair + 1], a, b[2], b[3]);
+            }
+        }
+        // ---- the rows' maximum and sum; weights in bfloat16 as the next product's operand
+        uint32_t p[4][4];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int limit = position[half] - tile * KEYS - 2 * t;     // key j * 8 + x <= limit
+            float highest = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                s[j][2 * half] = j * 8 <= limit ? s[j][2 * half] * factor : -INFINITY;
+                s[j][2 * half + 1] = j * 8 + 1 <= limit ? s[j][2 * half + 1] * factor : -INFINITY;
+                highest = fmaxf(highest, fmaxf(s[j][2 * half], s[j][2 * half + 1]));
+            }
+            highest = fmaxf(quad_max(highest), peak[half]);
+            const float base = highest == -INFINITY ? 0.f : highest;
+            const float shrink = exp2f(peak[half] - base);
+            peak[half] = highest;
+            float sum = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float a = exp2f(s[j][2 * half] - base), b = exp2f(s[j][2 * half + 1] - base);
+                sum += a + b;
+                p[j >> 1][half + 2 * (j & 1)] = pack_bf16(a, b);
+            }
+            total[half] = total[half] * shrink + quad_sum(sum);
+#pragma unroll
+            for (int j = 0; j < LONG_TILES; ++j) {
+                o[j][2 * half] *= shrink;
+                o[j][2 * half + 1] *= shrink;
+            }
+        }
+        // ---- the warp's columns of the output
+#pragma unroll
+        for (int j = 0; j < LONG_TILES; ++j) {
+            const int column = (side * LONG_TILES + j) * 8;
+            if (column < latent) {
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t b[4];
+                    ldmatrix_x4_trans(b, keys + (32 * half + lane) * stride + column);
+                    mma_16816(o[j], p[2 * half], b[0], b[1]);
+                    mma_16816(o[j], p[2 * half + 1], b[2], b[3]);
+                }
+            }
+        }
+    }
+    copy_wait<0>();
+
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int row = group * 16 + g + 8 * half;
+        if (row >= live_rows) continue;
+        const size_t global_row = first_row + row;
+        const float inverse = total[half] > 0.f ? 1.f / total[half] : 0.f;
+#pragma unroll
+        for (int j = 0; j < LONG_TILES; ++j) {
+            const int column = (side * LONG_TILES + j) * 8 + 2 * t;
+            if (column < latent)
+                *reinterpret_cast<uint32_t*>(out + global_row * row_size + column) =
+                    pack_bf16(o[j][2 * half] * inverse, o[j][2 * half + 1] * inverse);
+        }
+    }
+}
+
+template <int C>
+size_t long_shared_bytes(int row_size) {
+    const int stride = ((row_size + 15) & ~15) + 8;
+    return (size_t)(16 * (WARPS / C) + 2 * KEYS) * stride * sizeof(bf16);
+}
+
+template <int C>
+int launch_latent_long(const bf16* q, const bf16* pages, const int* block_table, int table_width,
+                       int page_size, const int* positions, const int* request_start, bf16* out,
+                       int requests, int max_rows, int heads, int row_size, int latent, float scale,
+                       int* error_flag, cudaStream_t stream) {
+    constexpr int ROWS = 16 * (WARPS / C);
+    static bool prepared = false;
+    if (!prepared) {
+        cudaError_t err = cudaFuncSetAttribute(latent_attention_long_kernel<C>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)MAX_SHARED);
+        MLXONE_REQUIRE(err == cudaSuccess, "latent attention: %s", cudaGetErrorString(err));
+        prepared = true;
+    }
+    const dim3 grid((max_rows + ROWS - 1) / ROWS, requests);
+    latent_attention_long_kernel<C><<<grid, WARPS * 32, long_shared_bytes<C>(row_size), stream>>>(
+        q, pages, block_table, table_width, page_size, positions, request_start, out, heads,
+        row_size, latent, scale, error_flag);
+    MLXONE_LAUNCH_CHECK("latent_attention_long");
+    return 0;
+}
+
 // One block per row: out = sum_s 2^(max_s - max) partial_s / sum_s 2^(max_s - max) sum_s.
 __global__ void __launch_bounds__(128)
 latent_merge_kernel(const float* __restrict__ partial, const float* __restrict__ stats,
@@ -351,8 +548,8 @@ template <int MT>
 int launch_latent(const bf16* q, const bf16* pages, const int* block_table, int table_width,
                   int page_size, const int* positions, const int* request_start, bf16* out,
                   float* partial, float* stats, int total_rows, int requests, int max_rows,
-                  int heads, int row_size, int latent, float scale, int splits, int* error_flag,
-                  cudaStream_t stream) {
+                  int heads, int row_size, int latent, float scale, int splits, int row_limit,
+                  int* error_flag, cudaStream_t stream) {
     constexpr int ROWS = 16 * MT;
     const int stride = ((row_size + 15) & ~15) + 8;
     const size_t shared = (size_t)(ROWS + 2 * KEYS) * stride * sizeof(bf16) +
@@ -369,7 +566,7 @@ int launch_latent(const bf16* q, const bf16* pages, const int* block_table, int 
     const dim3 grid((max_rows + ROWS - 1) / ROWS, requests, splits);
     latent_attention_kernel<MT><<<grid, WARPS * 32, shared, stream>>>(
         q, pages, block_table, table_width, page_size, positions, request_start, out, partial,
-        stats, total_rows, heads, row_size, latent, scale, splits, error_flag);
+        stats, total_rows, heads, row_size, latent, scale, splits, row_limit, error_flag);
     MLXONE_LAUNCH_CHECK("latent_attention_mma");
     return 0;
 }
@@ -402,17 +599,33 @@ MLXONE_API int mlxone_latent_attention_mma(const void* q, const void* pages, con
     float* partial = scratch;
     float* stats = scratch ? scratch + (size_t)splits * total_rows * latent : nullptr;
     const long long max_rows = (long long)max_portion * heads;
-    int status;
-    if (max_rows > 16)
+    int status = 0;
+    int row_limit = 0;
+    if (splits == 1 && max_rows >= LONG_ROWS) {
+        // requests that bring many rows: the kernel whose warps own rows; the others (single
+        // tokens beside a prompt's portion) stay with the kernel whose warps share the keys
+        const bool halves = latent > 8 * LONG_TILES || long_shared_bytes<1>(row_size) > MAX_SHARED;
+        status = halves
+            ? launch_latent_long<2>((const bf16*)q, (const bf16*)pages, block_table, table_width,
+                                    page_size, positions, request_start, (bf16*)out, requests,
+                                    (int)max_rows, heads, row_size, latent, scale, error_flag, stream)
+            : launch_latent_long<1>((const bf16*)q, (const bf16*)pages, block_table, table_width,
+                                    page_size, positions, request_start, (bf16*)out, requests,
+                                    (int)max_rows, heads, row_size, latent, scale, error_flag, stream);
+        if (status || requests == 1) return status;
+        row_limit = LONG_ROWS;
+    }
+    const int short_rows = row_limit > 0 ? row_limit - 1 : (int)max_rows;
+    if (short_rows > 16)
         status = launch_latent<2>((const bf16*)q, (const bf16*)pages, block_table, table_width,
                                   page_size, positions, request_start, (bf16*)out, partial, stats,
-                                  total_rows, requests, (int)max_rows, heads, row_size, latent,
-                                  scale, splits, error_flag, stream);
+                                  total_rows, requests, short_rows, heads, row_size, latent,
+                                  scale, splits, row_limit, error_flag, stream);
     else
         status = launch_latent<1>((const bf16*)q, (const bf16*)pages, block_table, table_width,
                                   page_size, positions, request_start, (bf16*)out, partial, stats,
-                                  total_rows, requests, (int)max_rows, heads, row_size, latent,
-                                  scale, splits, error_flag, stream);
+                                  total_rows, requests, short_rows, heads, row_size, latent,
+                                  scale, splits, row_limit, error_flag, stream);
     if (status) return status;
     if (splits > 1) {
         latent_merge_kernel<<<total_rows, 128, 0, stream>>>(partial, stats, (bf16*)out, total_rows,

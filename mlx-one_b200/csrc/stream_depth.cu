@@ -99,88 +99,104 @@ __global__ void stream_average_kernel(const float* __restrict__ kept, long long 
 // out[t, c] = x[t, c] + sum_j w[c, j] * x[t - taps + 1 + j, c] over the tokens of t's request,
 // with the taps - 1 rows before the step's first token taken from the request's slot
 // (state[slot, k, c]: the row taps - 1 - k tokens before the step's first; zero before the
-// sequence's start, because a fresh slot is zero). A thread owns one channel of a run of
-// CONV_TOKENS tokens and carries the last taps - 1 inputs in registers. The thread of a
-// request's first token of the step is the only one that reads the slot's channel; it then
+// sequence's start, because a fresh slot is zero). A thread owns VEC neighbouring channels of
+// one token. A token with taps - 1 tokens of its request before it in the step reads rows of
+// the step only. The first taps - 1 tokens of a request in the step belong to the thread of the
+// first one: it is the only one that reads the slot's channels, and after the last read it
 // stores the last taps - 1 inputs of the step there.
-constexpr int CONV_TOKENS = 16;
 constexpr int MAX_TAPS = 16;
 
-template <typename T>
-__global__ void __launch_bounds__(128)
+template <int VEC>
+__device__ __forceinline__ void load_values(float (&v)[VEC], const float* p) {
+    if constexpr (VEC == 4) {
+        const float4 q = *reinterpret_cast<const float4*>(p);
+        v[0] = q.x, v[1] = q.y, v[2] = q.z, v[3] = q.w;
+    } else {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) v[i] = p[i];
+    }
+}
+
+template <typename T, int VEC>
+__device__ __forceinline__ void store_values(T* p, const float (&v)[VEC]) {
+    if constexpr (VEC == 4 && sizeof(T) == 4) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    } else if constexpr (VEC == 4 && sizeof(T) == 2) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]);
+        const __nv_bfloat162 hi = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 packed;
+        packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(p) = packed;
+    } else {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) p[i] = from_float<T>(v[i]);
+    }
+}
+
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256)
 stream_conv_kernel(const float* __restrict__ x, const float* __restrict__ kernel, int taps,
                    const int* __restrict__ token_request, const int* __restrict__ request_start,
-                   float* __restrict__ state, long long slot_stride, const int* __restrict__ slots,
+                   float* state, long long slot_stride, const int* __restrict__ slots,
                    T* __restrict__ out, int tokens, int hidden, int write) {
     griddep_launch();
     griddep_wait();
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= hidden) return;
-    const int t0 = blockIdx.y * CONV_TOKENS;
-    const int t1 = min(t0 + CONV_TOKENS, tokens);
+    const int per_row = hidden / VEC;
+    const long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (index >= (long long)tokens * per_row) return;
+    const int t = (int)(index / per_row);
+    const int c = (int)(index - (long long)t * per_row) * VEC;
+    const int r = token_request[t];
+    const int first = request_start[r];
     const int before = taps - 1;
-    float w[MAX_TAPS], window[MAX_TAPS];            // window[k]: the input before - k tokens back
+    const int place = t - first;
+    if (place > 0 && place < before) return;        // the thread of the request's first token has it
+    const float* w = kernel + (size_t)c * taps;     // channel c + v, tap j: w[v * taps + j]
+    float now[VEC], acc[VEC], in[VEC];
+    if (place >= before) {
+        load_values<VEC>(now, x + (size_t)t * hidden + c);
 #pragma unroll
-    for (int j = 0; j < MAX_TAPS; ++j) w[j] = j < taps ? kernel[(size_t)c * taps + j] : 0.f;
-    // The tokens that read a slot (the first taps - 1 of a request in this step) all belong to
-    // the thread of the request's first token, also where they lie in the next run: no other
-    // thread reads the slot's channel, which that thread overwrites. A thread therefore goes on
-    // beyond its run only through early tokens of requests that start inside the run.
-    int request = -1, last = -2;
-    for (int t = t0; t < tokens; ++t) {
-        const int r = token_request[t];
-        const int first = request_start[r];
-        const bool early = t - first < before;
-        if (t < t1) {
-            if (early && first < t0) continue;                   // the run before this one has it
-        } else if (!(early && first >= t0 && first < t1)) {
-            break;                       // (a request that starts in the next run is that run's)
+        for (int v = 0; v < VEC; ++v) acc[v] = now[v];
+        for (int k = 0; k < before; ++k) {
+            load_values<VEC>(in, x + (size_t)(t - before + k) * hidden + c);
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) acc[v] = fmaf(w[v * taps + k], in[v], acc[v]);
         }
-        if (r != request || t != last + 1) {
-            request = r;
-            float* slot = state != nullptr ? state + slots[r] * slot_stride + c : nullptr;
-            // the inputs before token t: rows of this step, or of the slot
 #pragma unroll
-            for (int k = 0; k < MAX_TAPS; ++k) {
-                if (k >= before) continue;
-                const int source = t - before + k;
-                window[k] = source >= first ? x[(size_t)source * hidden + c]
-                                            : slot[(size_t)(before - (first - source)) * hidden];
-            }
-            if (t == first && write && slot != nullptr) {
-                // what the next step finds: the last `before` inputs after this step's n tokens
-                const int n = request_start[r + 1] - first;
+        for (int v = 0; v < VEC; ++v) acc[v] = fmaf(w[v * taps + before], now[v], acc[v]);
+        store_values<T, VEC>(out + (size_t)t * hidden + c, acc);
+        return;
+    }
+    // the request's first token of the step (and taps > 1): its first taps - 1 tokens, and the slot
+    const int n = request_start[r + 1] - first;
+    float* slot = state + slots[r] * slot_stride + c;
+    const int early = min(n, before);
+    for (int e = 0; e < early; ++e) {
+        load_values<VEC>(now, x + (size_t)(first + e) * hidden + c);
 #pragma unroll
-                for (int k = 0; k < MAX_TAPS; ++k) {
-                    if (k >= before) continue;
-                    const int e = n - before + k;              // relative to the step's first token
-                    // (e < 0: a row of the old slot, which `window` holds: row k + n)
-                    float v = 0.f;
-                    if (e >= 0) {
-                        v = x[(size_t)(first + e) * hidden + c];
-                    } else {
+        for (int v = 0; v < VEC; ++v) acc[v] = now[v];
+        for (int k = 0; k < before; ++k) {
+            const int back = e - before + k;         // relative to the step's first token
+            load_values<VEC>(in, back >= 0 ? x + (size_t)(first + back) * hidden + c
+                                           : slot + (size_t)(before + back) * hidden);
 #pragma unroll
-                        for (int q = 0; q < MAX_TAPS; ++q)
-                            if (q == k + n) v = window[q];
-                    }
-                    slot[(size_t)k * hidden] = v;
-                }
-            }
+            for (int v = 0; v < VEC; ++v) acc[v] = fmaf(w[v * taps + k], in[v], acc[v]);
         }
-        last = t;
-        const float now = x[(size_t)t * hidden + c];
-        float acc = now;
 #pragma unroll
-        for (int k = 0; k < MAX_TAPS; ++k)
-            if (k < before) acc = fmaf(w[k], window[k], acc);
-        acc = fmaf(w[before], now, acc);
-        out[(size_t)t * hidden + c] = from_float<T>(acc);
-#pragma unroll
-        for (int k = 0; k < MAX_TAPS - 1; ++k)
-            if (k < before - 1) window[k] = window[k + 1];
-#pragma unroll
-        for (int k = 0; k < MAX_TAPS; ++k)
-            if (k == before - 1) window[k] = now;
+        for (int v = 0; v < VEC; ++v) acc[v] = fmaf(w[v * taps + before], now[v], acc[v]);
+        store_values<T, VEC>(out + (size_t)(first + e) * hidden + c, acc);
+    }
+    if (write) {
+        // what the next step finds: the last `before` inputs after this step's n tokens. Row k
+        // takes a row of the step or, of a short step, the old row k + n, which lies behind
+        // it and is still the old one while the rows are written in rising order.
+        for (int k = 0; k < before; ++k) {
+            const int e = n - before + k;
+            load_values<VEC>(in, e >= 0 ? x + (size_t)(first + e) * hidden + c
+                                        : slot + (size_t)(k + n) * hidden);
+            store_values<float, VEC>(slot + (size_t)k * hidden, in);
+        }
     }
 }
 
@@ -260,16 +276,24 @@ MLXONE_API int mlxone_stream_conv(const float* x, const float* kernel, int taps,
     MLXONE_REQUIRE(taps >= 1 && taps <= MAX_TAPS, "stream_conv: 1 to %d taps, got %d", MAX_TAPS, taps);
     MLXONE_REQUIRE(taps == 1 || (state != nullptr && slots != nullptr),
                    "stream_conv: more than one tap needs the requests' slots");
-    const dim3 grid(ceil_div_host(hidden, 128), ceil_div_host(tokens, CONV_TOKENS));
-    MLXONE_REQUIRE(grid.y <= 65535, "stream_conv: too many tokens (%d)", tokens);
-    if (dtype == MLXONE_BF16)
-        launch_kernel(stream_conv_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, true, x, kernel,
-                      taps, token_request, request_start, state, slot_stride, slots,
-                      (__nv_bfloat16*)out, tokens, hidden, write);
-    else
-        launch_kernel(stream_conv_kernel<float>, grid, dim3(128), 0, stream, true, x, kernel, taps,
-                      token_request, request_start, state, slot_stride, slots, (float*)out, tokens,
-                      hidden, write);
+    const bool wide = hidden % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                      (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
+                      (state == nullptr || ((reinterpret_cast<uintptr_t>(state) & 15) == 0 &&
+                                            slot_stride % 4 == 0));
+    const long long threads = (long long)tokens * (wide ? hidden / 4 : hidden);
+    const dim3 grid((unsigned)ceil_div_host(threads, 256));
+#define MLXONE_STREAM_CONV(T, VEC)                                                                \
+    launch_kernel(stream_conv_kernel<T, VEC>, grid, dim3(256), 0, stream, true, x, kernel, taps,  \
+                  token_request, request_start, state, slot_stride, slots, (T*)out, tokens,       \
+                  hidden, write)
+    if (dtype == MLXONE_BF16) {
+        if (wide) MLXONE_STREAM_CONV(__nv_bfloat16, 4);
+        else MLXONE_STREAM_CONV(__nv_bfloat16, 1);
+    } else {
+        if (wide) MLXONE_STREAM_CONV(float, 4);
+        else MLXONE_STREAM_CONV(float, 1);
+    }
+#undef MLXONE_STREAM_CONV
     MLXONE_LAUNCH_CHECK("stream_conv");
     return 0;
 }
