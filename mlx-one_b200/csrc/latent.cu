@@ -102,6 +102,32 @@ __global__ void sigmoid_gate_kernel(const T* __restrict__ values, const T* __res
     out[i] = from_float<T>(to_float<T>(values[i]) / (1.f + expf(-g)));
 }
 
+// The same for bfloat16 rows whose width and strides are multiples of 8: 16 bytes per thread.
+__global__ void sigmoid_gate_wide_kernel(const __nv_bfloat16* __restrict__ values,
+                                         const __nv_bfloat16* __restrict__ gate, int ld_gate,
+                                         __nv_bfloat16* __restrict__ out, int width,
+                                         long long groups) {
+    griddep_launch();
+    griddep_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= groups) return;
+    const int per_row = width >> 3;
+    const long long t = i / per_row;
+    const int c = (int)(i - t * per_row) << 3;
+    const uint4 v = *reinterpret_cast<const uint4*>(values + t * width + c);
+    const uint4 g = *reinterpret_cast<const uint4*>(gate + t * ld_gate + c);
+    const __nv_bfloat162* vs = reinterpret_cast<const __nv_bfloat162*>(&v);
+    const __nv_bfloat162* gs = reinterpret_cast<const __nv_bfloat162*>(&g);
+    uint4 result;
+    __nv_bfloat162* rs = reinterpret_cast<__nv_bfloat162*>(&result);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 a = __bfloat1622float2(vs[j]), b = __bfloat1622float2(gs[j]);
+        rs[j] = __floats2bfloat162_rn(a.x / (1.f + expf(-b.x)), a.y / (1.f + expf(-b.y)));
+    }
+    *reinterpret_cast<uint4*>(out + t * width + c) = result;
+}
+
 // maps [tokens, 2 * heads, row_dim]: head h of map m is row m * heads + h, its first value_dim
 // values count. out [tokens, heads * value_dim]: o = a1 - mix * a2, o * rsqrt(mean(o^2) + eps) *
 // factor. One warp per (token, head).
@@ -183,7 +209,14 @@ MLXONE_API int mlxone_sigmoid_gate(const void* values, const void* gate, int ld_
     if (rows == 0 || width == 0) return 0;
     MLXONE_REQUIRE(rows > 0 && width > 0 && ld_gate >= width, "sigmoid_gate: bad sizes");
     const long long total = (long long)rows * width;
-    if (dtype == MLXONE_BF16) {
+    const auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    if (dtype == MLXONE_BF16 && width % 8 == 0 && ld_gate % 8 == 0 && aligned(values) &&
+        aligned(gate) && aligned(out)) {
+        using T = __nv_bfloat16;
+        launch_kernel(sigmoid_gate_wide_kernel, dim3(ceil_div_host(total / 8, 256)), dim3(256), 0,
+                      stream, true, (const T*)values, (const T*)gate, ld_gate, (T*)out, width,
+                      total / 8);
+    } else if (dtype == MLXONE_BF16) {
         using T = __nv_bfloat16;
         launch_kernel(sigmoid_gate_kernel<T>, dim3(ceil_div_host(total, 256)), dim3(256), 0, stream,
                       true, (const T*)values, (const T*)gate, ld_gate, (T*)out, width, total);

@@ -79,24 +79,26 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // Copies keys first..first+63 of a request into a tile [64][stride]; rows beyond `last` or
-// without a page are zero.
+// without a page are zero. A warp copies every eighth row, its lanes the row's 16-byte pieces.
 __device__ __forceinline__ void load_keys(bf16* tile, int stride, const bf16* pages,
                                           const int* table, int table_width, int page_size,
                                           int row_size, int first, int last, int* error_flag) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int chunks = row_size >> 3;
-    for (int piece = threadIdx.x; piece < KEYS * chunks; piece += WARPS * 32) {
-        const int row = piece / chunks, chunk = piece - row * chunks;
+    for (int row = warp; row < KEYS; row += WARPS) {
         const int key = first + row;
         bool live = key <= last;
-        size_t offset = 0;
+        const bf16* source = pages;
         if (live) {
             const int block = key / page_size;
             const int page = block < table_width ? table[block] : -1;
             live = page >= 0;
-            if (live) offset = ((size_t)page * page_size + (key - block * page_size)) * row_size + chunk * 8;
-            else if (chunk == 0) atomicExch(error_flag, 3);
+            if (live) source = pages + ((size_t)page * page_size + (key - block * page_size)) * row_size;
+            else if (lane == 0) atomicExch(error_flag, 3);
         }
-        copy16(tile + row * stride + chunk * 8, pages + offset, live);
+        bf16* target = tile + row * stride;
+        for (int chunk = lane; chunk < chunks; chunk += 32)
+            copy16(target + chunk * 8, source + (live ? chunk * 8 : 0), live);
     }
 }
 
@@ -518,29 +520,39 @@ int launch_latent_long(const bf16* q, const bf16* pages, const int* block_table,
     return 0;
 }
 
-// One block per row: out = sum_s 2^(max_s - max) partial_s / sum_s 2^(max_s - max) sum_s.
+// One block per row: out = sum_s 2^(max_s - max) partial_s / sum_s 2^(max_s - max) sum_s. The
+// splits' factors are worked out once (a lane per split) and left in shared memory.
+constexpr int MAX_SPLITS = 32;
+
 __global__ void __launch_bounds__(128)
 latent_merge_kernel(const float* __restrict__ partial, const float* __restrict__ stats,
                     bf16* __restrict__ out, int total_rows, int row_size, int latent, int splits) {
+    __shared__ float factors[MAX_SPLITS];
     const int row = blockIdx.x;
-    float highest = -INFINITY;
-    for (int s = 0; s < splits; ++s)
-        highest = fmaxf(highest, stats[2 * ((size_t)s * total_rows + row)]);
-    float sum = 0.f;
-    for (int s = 0; s < splits; ++s) {
-        const size_t at = (size_t)s * total_rows + row;
-        const float peak = stats[2 * at];
-        if (peak != -INFINITY) sum += exp2f(peak - highest) * stats[2 * at + 1];
+    if (threadIdx.x < 32) {
+        const int s = threadIdx.x;
+        float peak = -INFINITY, sum = 0.f;
+        if (s < splits) {
+            const float2 both = *reinterpret_cast<const float2*>(stats + 2 * ((size_t)s * total_rows + row));
+            peak = both.x, sum = both.y;
+        }
+        float highest = peak;
+#pragma unroll
+        for (int step = 16; step > 0; step >>= 1)
+            highest = fmaxf(highest, __shfl_xor_sync(0xffffffffu, highest, step));
+        const float weight = peak == -INFINITY ? 0.f : exp2f(peak - highest);
+        float all = weight * sum;
+#pragma unroll
+        for (int step = 16; step > 0; step >>= 1) all += __shfl_xor_sync(0xffffffffu, all, step);
+        factors[s] = all > 0.f ? weight / all : 0.f;
     }
-    const float inverse = sum > 0.f ? 1.f / sum : 0.f;
+    __syncthreads();
     for (int column = threadIdx.x; column < latent; column += blockDim.x) {
         float value = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const size_t at = (size_t)s * total_rows + row;
-            const float peak = stats[2 * at];
-            if (peak != -INFINITY) value += exp2f(peak - highest) * partial[at * latent + column];
-        }
-        out[(size_t)row * row_size + column] = __float2bfloat16_rn(value * inverse);
+#pragma unroll 4
+        for (int s = 0; s < splits; ++s)
+            value = fmaf(factors[s], partial[((size_t)s * total_rows + row) * latent + column], value);
+        out[(size_t)row * row_size + column] = __float2bfloat16_rn(value);
     }
 }
 
@@ -593,7 +605,8 @@ MLXONE_API int mlxone_latent_attention_mma(const void* q, const void* pages, con
                    "latent attention: rows of %d with %d latent values do not fit", row_size, latent);
     MLXONE_REQUIRE(requests > 0 && heads > 0 && max_portion > 0 && page_size > 0 && table_width > 0,
                    "latent attention: bad sizes");
-    MLXONE_REQUIRE(splits >= 1 && (splits == 1 || (max_portion == 1 && scratch != nullptr)),
+    MLXONE_REQUIRE(splits >= 1 && splits <= MAX_SPLITS &&
+                       (splits == 1 || (max_portion == 1 && scratch != nullptr)),
                    "latent attention: keys are split only in steps of single tokens");
     const int total_rows = tokens * heads;
     float* partial = scratch;

@@ -619,7 +619,7 @@ class CudaOps:
             # steps of single tokens cut the keys into runs that fill the GPU, merged afterwards
             splits, scratch = 1, None
             if ctx.max_portion == 1:
-                blocks = ctx.requests * -(-heads // 16)
+                blocks = ctx.requests * (1 if heads <= 16 else -(-heads // 32))
                 bound = min(ctx.max_context, view.block_table.shape[1] * view.page_size)
                 splits = max(1, min(self._sm_count // blocks, -(-bound // 64) // 2, 32))
                 if splits > 1:
