@@ -1669,6 +1669,23 @@ def kernel_case(name: str, batch: int, context: int) -> int:
                          write=True, heads=heads, key_dim=key_dim, value_dim=value_dim)
         run = lambda i: ops.lightning_attention(rows[i % 4], view=views[i % 4], **constants)
         work = f"{ctx.tokens} tokens of {len(portions)} requests, {heads} heads of {key_dim} x {value_dim}, state {slot * 4 / 1e6:.1f} MB a request"
+    elif name in ("latent_prefill", "latent_decode"):
+        # attention over latent rows at the sizes of a Lamisun 1024 wide: one 2,048-token prompt
+        # (the kernel whose warps own 16 rows) or `batch` single tokens (key runs and their merge)
+        mixer = lamisun_shape(1024, 1)["layers"][0]["mixer"]
+        rot, latent = mixer["rot_dim"], mixer["kv_rank"]
+        row = latent + rot
+        portions = [PREFILL_TOKENS] if name == "latent_prefill" else [1] * batch
+        ctx, plain = batch_context(portions, [0 if name == "latent_prefill" else context] * len(portions))
+        pages = (torch.randn(1, int(plain.block_table.max()) + 1, 1, PAGE_SIZE, row, device=device)
+                 * 0.3).bfloat16()
+        view = PagedView(pages, plain.block_table, PAGE_SIZE, PagedKeyValues(1, row, planes=1))
+        queries = [(torch.randn(ctx.tokens, mixer["heads"], row, device=device) * 0.3).bfloat16()
+                   for _ in range(4)]
+        run = lambda i: ops.latent_attention(queries[i % 4], heads=mixer["heads"], latent=latent,
+                                             scale=mixer["scale"], ctx=ctx, view=view)
+        work = (f"{ctx.tokens} tokens of {len(portions)} requests, {mixer['heads']} heads, rows of "
+                f"{latent} + {rot}, keys {pages.numel() * 2 / 1e6:.1f} MB")
     else:
         print(f"unknown kernel case {name!r}")
         return 2
@@ -1777,7 +1794,7 @@ def main() -> int:
                         help="run one kernel alone instead of the benchmark: skinny_swiglu, "
                              "skinny_in_proj, skinny_down, decode_attention, prefill_attention, tcgen05_swiglu, "
                              "swapped_swiglu, mixed_attention, sampling, delta_prefill, delta_decode, lightning_prefill, "
-                             "lightning_decode, experts_sorted, decode_step (the "
+                             "lightning_decode, experts_sorted, latent_prefill, latent_decode, decode_step (the "
                              "whole step, eager, for a launch list), decode_timeline (where "
                              "the graph-replayed step's time goes, kernel by kernel)")
     parser.add_argument("--dependent-launches", type=int, default=1,

@@ -204,15 +204,32 @@ latent_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
         for (int m = 0; m < MT; ++m) s[m][0] = s[m][1] = s[m][2] = s[m][3] = 0.f;
         const bf16* key_rows = keys + (warp * 8 + (lane & 7)) * stride + ((lane >> 3) & 1) * 8;
         const bf16* query_rows = q_tile + (lane & 15) * stride + (lane >> 4) * 8;
-#pragma unroll 4
-        for (int k0 = 0; k0 < padded; k0 += 16) {
-            uint32_t b[2];
-            ldmatrix_x2(b, key_rows + k0);
+        // (the next step's operands are asked for before this step's products are issued)
+        {
+            uint32_t b[2], a[MT][4];
+            ldmatrix_x2(b, key_rows);
 #pragma unroll
-            for (int m = 0; m < MT; ++m) {
-                uint32_t a[4];
-                ldmatrix_x4(a, query_rows + m * 16 * stride + k0);
-                mma_16816(s[m], a, b[0], b[1]);
+            for (int m = 0; m < MT; ++m) ldmatrix_x4(a[m], query_rows + m * 16 * stride);
+#pragma unroll 4
+            for (int k0 = 0; k0 < padded; k0 += 16) {
+                uint32_t nb[2] = {b[0], b[1]}, na[MT][4];
+#pragma unroll
+                for (int m = 0; m < MT; ++m)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) na[m][i] = a[m][i];
+                if (k0 + 16 < padded) {
+                    ldmatrix_x2(nb, key_rows + k0 + 16);
+#pragma unroll
+                    for (int m = 0; m < MT; ++m)
+                        ldmatrix_x4(na[m], query_rows + m * 16 * stride + k0 + 16);
+                }
+#pragma unroll
+                for (int m = 0; m < MT; ++m) mma_16816(s[m], a[m], b[0], b[1]);
+                b[0] = nb[0], b[1] = nb[1];
+#pragma unroll
+                for (int m = 0; m < MT; ++m)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) a[m][i] = na[m][i];
             }
         }
         const int key0 = tile * KEYS + warp * 8 + 2 * t;
@@ -270,19 +287,27 @@ latent_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
         }
 
         // ---- this warp's columns of the output
+        {
+            uint32_t b[4] = {0u, 0u, 0u, 0u};
+            if (warp * 8 < latent) ldmatrix_x4_trans(b, keys + lane * stride + warp * 8);
 #pragma unroll
-        for (int j = 0; j < GROUPS; ++j) {
-            const int column = (warp + WARPS * j) * 8;
-            if (column < latent) {
+            for (int j = 0; j < GROUPS; ++j) {
+                const int column = (warp + WARPS * j) * 8;
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
-                    uint32_t b[4];
-                    ldmatrix_x4_trans(b, keys + (32 * half + lane) * stride + column);
+                    uint32_t nb[4] = {b[0], b[1], b[2], b[3]};
+                    const int next_column = half == 0 ? column : column + WARPS * 8;
+                    if ((half == 0 || j + 1 < GROUPS) && next_column < latent)
+                        ldmatrix_x4_trans(nb, keys + (32 * (1 - half) + lane) * stride + next_column);
+                    if (column < latent) {
 #pragma unroll
-                    for (int m = 0; m < MT; ++m) {
-                        mma_16816(o[m][j], p[m][2 * half], b[0], b[1]);
-                        mma_16816(o[m][j], p[m][2 * half + 1], b[2], b[3]);
+                        for (int m = 0; m < MT; ++m) {
+                            mma_16816(o[m][j], p[m][2 * half], b[0], b[1]);
+                            mma_16816(o[m][j], p[m][2 * half + 1], b[2], b[3]);
+                        }
                     }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) b[i] = nb[i];
                 }
             }
         }
@@ -417,16 +442,30 @@ latent_attention_long_kernel(const bf16* __restrict__ q, const bf16* __restrict_
         for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
         const bf16* key_rows = keys + ((lane & 7) + ((lane >> 4) << 3)) * stride +
                                ((lane >> 3) & 1) * 8;
+        // (the next operands are asked for before the products on the present ones are issued)
+        {
+            uint32_t a[4], b[4];
+            ldmatrix_x4(a, query_rows);
+            ldmatrix_x4(b, key_rows);
 #pragma unroll 2
-        for (int k0 = 0; k0 < padded; k0 += 16) {
-            uint32_t a[4];
-            ldmatrix_x4(a, query_rows + k0);
+            for (int k0 = 0; k0 < padded; k0 += 16) {
+                uint32_t na[4] = {a[0], a[1], a[2], a[3]};
 #pragma unroll
-            for (int pair = 0; pair < 4; ++pair) {
-                uint32_t b[4];
-                ldmatrix_x4(b, key_rows + pair * 16 * stride + k0);
-                mma_16816(s[2 * pair], a, b[0], b[1]);
-                mma_16816(s[2 * pair + 1], a, b[2], b[3]);
+                for (int pair = 0; pair < 4; ++pair) {
+                    uint32_t nb[4] = {b[0], b[1], b[2], b[3]};
+                    if (pair < 3) {
+                        ldmatrix_x4(nb, key_rows + (pair + 1) * 16 * stride + k0);
+                    } else if (k0 + 16 < padded) {
+                        ldmatrix_x4(na, query_rows + k0 + 16);
+                        ldmatrix_x4(nb, key_rows + k0 + 16);
+                    }
+                    mma_16816(s[2 * pair], a, b[0], b[1]);
+                    mma_16816(s[2 * pair + 1], a, b[2], b[3]);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) b[i] = nb[i];
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) a[i] = na[i];
             }
         }
         // ---- the rows' maximum and sum; weights in bfloat16 as the next product's operand
@@ -460,16 +499,25 @@ latent_attention_long_kernel(const bf16* __restrict__ q, const bf16* __restrict_
             }
         }
         // ---- the warp's columns of the output
+        {
+            uint32_t b[4] = {0u, 0u, 0u, 0u};
+            if (side * LONG_TILES * 8 < latent)
+                ldmatrix_x4_trans(b, keys + lane * stride + side * LONG_TILES * 8);
 #pragma unroll
-        for (int j = 0; j < LONG_TILES; ++j) {
-            const int column = (side * LONG_TILES + j) * 8;
-            if (column < latent) {
+            for (int j = 0; j < LONG_TILES; ++j) {
+                const int column = (side * LONG_TILES + j) * 8;
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
-                    uint32_t b[4];
-                    ldmatrix_x4_trans(b, keys + (32 * half + lane) * stride + column);
-                    mma_16816(o[j], p[2 * half], b[0], b[1]);
-                    mma_16816(o[j], p[2 * half + 1], b[2], b[3]);
+                    uint32_t nb[4] = {b[0], b[1], b[2], b[3]};
+                    const int next_column = half == 0 ? column : column + 8;
+                    if ((half == 0 || j + 1 < LONG_TILES) && next_column < latent)
+                        ldmatrix_x4_trans(nb, keys + (32 * (1 - half) + lane) * stride + next_column);
+                    if (column < latent) {
+                        mma_16816(o[j], p[2 * half], b[0], b[1]);
+                        mma_16816(o[j], p[2 * half + 1], b[2], b[3]);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) b[i] = nb[i];
                 }
             }
         }

@@ -621,7 +621,11 @@ class CudaOps:
             if ctx.max_portion == 1:
                 blocks = ctx.requests * (1 if heads <= 16 else -(-heads // 32))
                 bound = min(ctx.max_context, view.block_table.shape[1] * view.page_size)
-                splits = max(1, min(self._sm_count // blocks, -(-bound // 64) // 2, 32))
+                # as many runs as blocks fit on the GPU at once, two tiles a run where there are two, and
+                # no run left without tiles (the kernel gives a run ceil(tiles / splits) tiles)
+                tiles = -(-bound // 64)
+                most = max(1, min(self._sm_count // blocks, -(-tiles // 2), 32))
+                splits = -(-tiles // -(-tiles // most))
                 if splits > 1:
                     scratch = torch.empty(splits * tokens * heads * (latent + 2),
                                           dtype=torch.float32, device=self.device)
