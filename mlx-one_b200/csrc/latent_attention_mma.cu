@@ -157,6 +157,12 @@ latent_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
         for (int i = threadIdx.x; i < (ROWS + 2 * KEYS) * extra; i += WARPS * 32)
             q_tile[(i / extra) * stride + row_size + i % extra] = __float2bfloat16_rn(0.f);
     }
+    // The keys were written before the kernel ahead of this one in the stream started (that
+    // kernel makes the queries), so the first tile is asked for before waiting for it.
+    if (tile_first < tile_end)
+        load_keys(k_tiles[0], stride, pages, table, table_width, page_size, row_size,
+                  tile_first * KEYS, last_key, error_flag);
+    griddep_wait();
     {
         const int chunks = row_size >> 3;
         for (int piece = threadIdx.x; piece < ROWS * chunks; piece += WARPS * 32) {
@@ -166,9 +172,6 @@ latent_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
                    q + (live ? (first_row + row) * row_size + chunk * 8 : 0), live);
         }
     }
-    if (tile_first < tile_end)
-        load_keys(k_tiles[0], stride, pages, table, table_width, page_size, row_size,
-                  tile_first * KEYS, last_key, error_flag);
     copy_commit();
 
     // the positions of this thread's rows (g and g + 8 of every 16)
@@ -492,33 +495,55 @@ latent_attention_long_kernel(const bf16* __restrict__ q, const bf16* __restrict_
                 p[j >> 1][half + 2 * (j & 1)] = pack_bf16(a, b);
             }
             total[half] = total[half] * shrink + quad_sum(sum);
+            // (a tile that raises no row's maximum leaves the warp's output as it is)
+            if (__any_sync(0xffffffffu, shrink != 1.f)) {
 #pragma unroll
-            for (int j = 0; j < LONG_TILES; ++j) {
-                o[j][2 * half] *= shrink;
-                o[j][2 * half + 1] *= shrink;
+                for (int j = 0; j < LONG_TILES; ++j) {
+                    o[j][2 * half] *= shrink;
+                    o[j][2 * half + 1] *= shrink;
+                }
             }
         }
         // ---- the warp's columns of the output
+        // Groups of four 8-column blocks: their four key fragments are asked for one group
+        // ahead, and products that follow one another go to different accumulators.
         {
-            uint32_t b[4] = {0u, 0u, 0u, 0u};
-            if (side * LONG_TILES * 8 < latent)
-                ldmatrix_x4_trans(b, keys + lane * stride + side * LONG_TILES * 8);
+            constexpr int PER = 4, COUNT = 2 * (LONG_TILES / PER);
+            uint32_t b[PER][4];
 #pragma unroll
-            for (int j = 0; j < LONG_TILES; ++j) {
-                const int column = (side * LONG_TILES + j) * 8;
+            for (int u = 0; u < PER; ++u) {
+                b[u][0] = b[u][1] = b[u][2] = b[u][3] = 0u;
+                const int column = (side * LONG_TILES + u) * 8;
+                if (column < latent) ldmatrix_x4_trans(b[u], keys + lane * stride + column);
+            }
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    uint32_t nb[4] = {b[0], b[1], b[2], b[3]};
-                    const int next_column = half == 0 ? column : column + 8;
-                    if ((half == 0 || j + 1 < LONG_TILES) && next_column < latent)
-                        ldmatrix_x4_trans(nb, keys + (32 * (1 - half) + lane) * stride + next_column);
-                    if (column < latent) {
-                        mma_16816(o[j], p[2 * half], b[0], b[1]);
-                        mma_16816(o[j], p[2 * half + 1], b[2], b[3]);
+            for (int turn = 0; turn < COUNT; ++turn) {
+                const int half = turn / (LONG_TILES / PER), first = (turn % (LONG_TILES / PER)) * PER;
+                uint32_t nb[PER][4];
+#pragma unroll
+                for (int u = 0; u < PER; ++u) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) nb[u][i] = b[u][i];
+                    if (turn + 1 < COUNT) {
+                        const int next_half = (turn + 1) / (LONG_TILES / PER);
+                        const int next_first = ((turn + 1) % (LONG_TILES / PER)) * PER;
+                        const int column = (side * LONG_TILES + next_first + u) * 8;
+                        if (column < latent)
+                            ldmatrix_x4_trans(nb[u], keys + (32 * next_half + lane) * stride + column);
                     }
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) b[i] = nb[i];
                 }
+#pragma unroll
+                for (int sub = 0; sub < 2; ++sub) {
+#pragma unroll
+                    for (int u = 0; u < PER; ++u) {
+                        if ((side * LONG_TILES + first + u) * 8 < latent)
+                            mma_16816(o[first + u], p[2 * half + sub], b[u][2 * sub], b[u][2 * sub + 1]);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < PER; ++u)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) b[u][i] = nb[u][i];
             }
         }
     }
@@ -577,6 +602,7 @@ latent_merge_kernel(const float* __restrict__ partial, const float* __restrict__
                     bf16* __restrict__ out, int total_rows, int row_size, int latent, int splits) {
     __shared__ float factors[MAX_SPLITS];
     const int row = blockIdx.x;
+    griddep_wait();
     if (threadIdx.x < 32) {
         const int s = threadIdx.x;
         float peak = -INFINITY, sum = 0.f;
@@ -624,9 +650,11 @@ int launch_latent(const bf16* q, const bf16* pages, const int* block_table, int 
         prepared = true;
     }
     const dim3 grid((max_rows + ROWS - 1) / ROWS, requests, splits);
-    latent_attention_kernel<MT><<<grid, WARPS * 32, shared, stream>>>(
-        q, pages, block_table, table_width, page_size, positions, request_start, out, partial,
-        stats, total_rows, heads, row_size, latent, scale, splits, row_limit, error_flag);
+    cudaError_t launched = launch_kernel(
+        latent_attention_kernel<MT>, grid, dim3(WARPS * 32), shared, stream, true, q, pages,
+        block_table, table_width, page_size, positions, request_start, out, partial, stats,
+        total_rows, heads, row_size, latent, scale, splits, row_limit, error_flag);
+    MLXONE_REQUIRE(launched == cudaSuccess, "latent attention: %s", cudaGetErrorString(launched));
     MLXONE_LAUNCH_CHECK("latent_attention_mma");
     return 0;
 }
@@ -689,8 +717,11 @@ MLXONE_API int mlxone_latent_attention_mma(const void* q, const void* pages, con
                                   scale, splits, row_limit, error_flag, stream);
     if (status) return status;
     if (splits > 1) {
-        latent_merge_kernel<<<total_rows, 128, 0, stream>>>(partial, stats, (bf16*)out, total_rows,
-                                                            row_size, latent, splits);
+        cudaError_t launched = launch_kernel(latent_merge_kernel, dim3(total_rows), dim3(128), 0,
+                                             stream, true, (const float*)partial,
+                                             (const float*)stats, (bf16*)out, total_rows, row_size,
+                                             latent, splits);
+        MLXONE_REQUIRE(launched == cudaSuccess, "latent merge: %s", cudaGetErrorString(launched));
         MLXONE_LAUNCH_CHECK("latent_merge");
     }
     return 0;

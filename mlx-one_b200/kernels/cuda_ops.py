@@ -609,7 +609,12 @@ class CudaOps:
     def latent_attention(self, queries, *, heads, latent, scale, ctx, view):
         """Causal softmax attention of queries [tokens, heads, row] over the one row per token in
         the request's single-plane pages, which is key and value at once. Returns [tokens, heads,
-        row]; the first ``latent`` values of a row are the weights' average of the latents."""
+        row]; the first ``latent`` values of a row are the weights' average of the latents.
+
+        The bfloat16 kernel is launched as a programmatic dependent of the kernel ahead of it in
+        the stream and asks for its first keys before it waits for that kernel: the rows in the
+        pages must be complete when that kernel starts (in a model it is the product that makes
+        the queries, which runs after the rows were written)."""
         tokens, _, row = queries.shape
         self._need(queries, view.kv.dtype, "queries")
         out = torch.empty((tokens, heads, row), dtype=queries.dtype, device=self.device)
