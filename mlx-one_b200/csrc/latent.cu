@@ -18,7 +18,7 @@ namespace {
 // of a rotated part; pair i is (2i, 2i + 1) if `neighbours`, else (i, i + rotary_dim / 2).
 // Dynamic shared memory: rotary_dim floats (cosines and sines).
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(512)
 latent_prepare_kernel(const T* __restrict__ projected, int ld, T* __restrict__ queries,
                       const float* __restrict__ norm_weight, float eps,
                       const float* __restrict__ inv_freq, int rotary_dim, int neighbours,
@@ -60,6 +60,7 @@ latent_prepare_kernel(const T* __restrict__ projected, int ld, T* __restrict__ q
         // (u, v) -> (u cos - v sin, v cos + u sin)
         return first ? v * cosines[pair] - w * sines[pair] : v * cosines[pair] + w * sines[pair];
     };
+#pragma unroll 4
     for (int i = threadIdx.x; i < heads * rot_dim; i += blockDim.x) {
         const int head = i / rot_dim, e = i % rot_dim;
         queries[((size_t)t * heads + head) * row + latent + e] =
@@ -187,15 +188,18 @@ MLXONE_API int mlxone_latent_prepare(const void* projected, int ld, void* querie
     MLXONE_REQUIRE(rotary_dim >= 0 && rotary_dim % 2 == 0 && rotary_dim <= rot_dim,
                    "latent_prepare: %d rotated dimensions in a part of %d", rotary_dim, rot_dim);
     const size_t shared = (size_t)rotary_dim * sizeof(float);
+    // (the block's size follows the model's sizes alone, so a token's sums never change order)
+    const int most = heads * rot_dim > latent ? heads * rot_dim : latent;
+    const int threads = most >= 2048 ? 512 : most >= 512 ? 256 : 128;
     if (dtype == MLXONE_BF16) {
         using T = __nv_bfloat16;
-        launch_kernel(latent_prepare_kernel<T>, dim3(tokens), dim3(128), shared, stream, true,
+        launch_kernel(latent_prepare_kernel<T>, dim3(tokens), dim3(threads), shared, stream, true,
                       (const T*)projected, ld, (T*)queries, norm_weight, eps, inv_freq, rotary_dim,
                       neighbours, positions, token_request, (T*)pages, block_table, table_width,
                       page_size, heads, head_dim, rot_dim, latent, write, error_flag);
     } else {
         using T = float;
-        launch_kernel(latent_prepare_kernel<T>, dim3(tokens), dim3(128), shared, stream, true,
+        launch_kernel(latent_prepare_kernel<T>, dim3(tokens), dim3(threads), shared, stream, true,
                       (const T*)projected, ld, (T*)queries, norm_weight, eps, inv_freq, rotary_dim,
                       neighbours, positions, token_request, (T*)pages, block_table, table_width,
                       page_size, heads, head_dim, rot_dim, latent, write, error_flag);

@@ -157,12 +157,16 @@ latent_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
         for (int i = threadIdx.x; i < (ROWS + 2 * KEYS) * extra; i += WARPS * 32)
             q_tile[(i / extra) * stride + row_size + i % extra] = __float2bfloat16_rn(0.f);
     }
-    // The keys were written before the kernel ahead of this one in the stream started (that
-    // kernel makes the queries), so the first tile is asked for before waiting for it.
-    if (tile_first < tile_end)
+    // Rows of earlier steps are in the pages whatever runs ahead of this kernel in the stream:
+    // a first tile that holds only such rows is asked for before waiting for that kernel.
+    const bool settled = tile_first * KEYS + KEYS <= history;
+    if (tile_first < tile_end && settled)
         load_keys(k_tiles[0], stride, pages, table, table_width, page_size, row_size,
                   tile_first * KEYS, last_key, error_flag);
     griddep_wait();
+    if (tile_first < tile_end && !settled)
+        load_keys(k_tiles[0], stride, pages, table, table_width, page_size, row_size,
+                  tile_first * KEYS, last_key, error_flag);
     {
         const int chunks = row_size >> 3;
         for (int piece = threadIdx.x; piece < ROWS * chunks; piece += WARPS * 32) {

@@ -134,7 +134,9 @@ __device__ __forceinline__ void store_values(T* p, const float (&v)[VEC]) {
     }
 }
 
-template <typename T, int VEC>
+// TAPS > 0: the number of taps is known when compiling, and a thread of four channels reads
+// its TAPS x 4 weights (which lie side by side) 16 bytes at a time into registers.
+template <typename T, int VEC, int TAPS>
 __global__ void __launch_bounds__(256)
 stream_conv_kernel(const float* __restrict__ x, const float* __restrict__ kernel, int taps,
                    const int* __restrict__ token_request, const int* __restrict__ request_start,
@@ -154,6 +156,30 @@ stream_conv_kernel(const float* __restrict__ x, const float* __restrict__ kernel
     if (place > 0 && place < before) return;        // the thread of the request's first token has it
     const float* w = kernel + (size_t)c * taps;     // channel c + v, tap j: w[v * taps + j]
     float now[VEC], acc[VEC], in[VEC];
+    if constexpr (TAPS > 0 && VEC == 4) {
+        if (place >= before) {
+            float held[VEC * TAPS];
+#pragma unroll
+            for (int i = 0; i < TAPS; ++i) {
+                const float4 four = reinterpret_cast<const float4*>(w)[i];
+                held[4 * i] = four.x, held[4 * i + 1] = four.y;
+                held[4 * i + 2] = four.z, held[4 * i + 3] = four.w;
+            }
+            load_values<VEC>(now, x + (size_t)t * hidden + c);
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) acc[v] = now[v];
+#pragma unroll
+            for (int k = 0; k < TAPS - 1; ++k) {
+                load_values<VEC>(in, x + (size_t)(t - (TAPS - 1) + k) * hidden + c);
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) acc[v] = fmaf(held[v * TAPS + k], in[v], acc[v]);
+            }
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) acc[v] = fmaf(held[v * TAPS + TAPS - 1], now[v], acc[v]);
+            store_values<T, VEC>(out + (size_t)t * hidden + c, acc);
+            return;
+        }
+    }
     if (place >= before) {
         load_values<VEC>(now, x + (size_t)t * hidden + c);
 #pragma unroll
@@ -282,17 +308,26 @@ MLXONE_API int mlxone_stream_conv(const float* x, const float* kernel, int taps,
                                             slot_stride % 4 == 0));
     const long long threads = (long long)tokens * (wide ? hidden / 4 : hidden);
     const dim3 grid((unsigned)ceil_div_host(threads, 256));
-#define MLXONE_STREAM_CONV(T, VEC)                                                                \
-    launch_kernel(stream_conv_kernel<T, VEC>, grid, dim3(256), 0, stream, true, x, kernel, taps,  \
-                  token_request, request_start, state, slot_stride, slots, (T*)out, tokens,       \
+#define MLXONE_STREAM_CONV(T, VEC, TAPS)                                                          \
+    launch_kernel(stream_conv_kernel<T, VEC, TAPS>, grid, dim3(256), 0, stream, true, x, kernel,  \
+                  taps, token_request, request_start, state, slot_stride, slots, (T*)out, tokens, \
                   hidden, write)
-    if (dtype == MLXONE_BF16) {
-        if (wide) MLXONE_STREAM_CONV(__nv_bfloat16, 4);
-        else MLXONE_STREAM_CONV(__nv_bfloat16, 1);
-    } else {
-        if (wide) MLXONE_STREAM_CONV(float, 4);
-        else MLXONE_STREAM_CONV(float, 1);
+#define MLXONE_STREAM_CONV_WIDE(T)                                                                \
+    switch ((reinterpret_cast<uintptr_t>(kernel) & 15) == 0 ? taps : 0) {                         \
+        case 2: MLXONE_STREAM_CONV(T, 4, 2); break;                                               \
+        case 3: MLXONE_STREAM_CONV(T, 4, 3); break;                                               \
+        case 4: MLXONE_STREAM_CONV(T, 4, 4); break;                                               \
+        case 5: MLXONE_STREAM_CONV(T, 4, 5); break;                                               \
+        default: MLXONE_STREAM_CONV(T, 4, 0);                                                     \
     }
+    if (dtype == MLXONE_BF16) {
+        if (wide) MLXONE_STREAM_CONV_WIDE(__nv_bfloat16)
+        else MLXONE_STREAM_CONV(__nv_bfloat16, 1, 0);
+    } else {
+        if (wide) MLXONE_STREAM_CONV_WIDE(float)
+        else MLXONE_STREAM_CONV(float, 1, 0);
+    }
+#undef MLXONE_STREAM_CONV_WIDE
 #undef MLXONE_STREAM_CONV
     MLXONE_LAUNCH_CHECK("stream_conv");
     return 0;

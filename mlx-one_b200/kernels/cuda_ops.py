@@ -612,9 +612,8 @@ class CudaOps:
         row]; the first ``latent`` values of a row are the weights' average of the latents.
 
         The bfloat16 kernel is launched as a programmatic dependent of the kernel ahead of it in
-        the stream and asks for its first keys before it waits for that kernel: the rows in the
-        pages must be complete when that kernel starts (in a model it is the product that makes
-        the queries, which runs after the rows were written)."""
+        the stream; before it waits for that kernel it reads ``ctx.positions``, the block table
+        and rows of positions before the step's first (rows that earlier steps wrote)."""
         tokens, _, row = queries.shape
         self._need(queries, view.kv.dtype, "queries")
         out = torch.empty((tokens, heads, row), dtype=queries.dtype, device=self.device)
