@@ -147,7 +147,9 @@ class CacheManager:
             return whole
         # keys of the last reach-1 positions, the step's own tokens, and one ragged edge
         step = min(self.max_step_tokens, tokens)
-        return min(whole, ceil_div(reach - 1 + step, self.page_size) + 1)
+        # ... and the pages of the first positions that stay visible behind a window
+        kept = ceil_div(group.need.keep_first, self.page_size)
+        return min(whole, ceil_div(reach - 1 + step, self.page_size) + 1 + kept)
 
     def fits_ever(self, tokens: int) -> bool:
         return all(self.pages_for(g, tokens) <= g.pool.count for g in self.paged)
@@ -242,7 +244,9 @@ class CacheManager:
                 # ... and nothing before the chunk that position ``length`` lies in
                 first_needed = max(first_needed, cache.length - cache.length % chunk)
             table = cache.tables[index]
-            for block in range(min(max(first_needed, 0) // self.page_size, len(table))):
+            # (pages that hold one of the first ``keep_first`` positions stay)
+            kept = ceil_div(group.need.keep_first, self.page_size)
+            for block in range(kept, min(max(first_needed, 0) // self.page_size, len(table))):
                 if table[block] >= 0:
                     group.pool.give_back(table[block])
                     table[block] = -1

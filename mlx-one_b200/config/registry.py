@@ -32,6 +32,7 @@ _BUILTIN = {
     "galarax": "mlx_one_b200.architectures.galarax:ARCHITECTURE",
     "farorax": "mlx_one_b200.architectures.farorax:ARCHITECTURE",
     "lamisun": "mlx_one_b200.architectures.lamisun:ARCHITECTURE",
+    "tirudra": "mlx_one_b200.architectures.tirudra:ARCHITECTURE",
 }
 _REGISTERED: dict[str, Architecture] = {}
 

@@ -6,7 +6,9 @@
 // positions, one key per lane; softmax statistics and the output are kept in 32-bit and
 // updated block by block (online softmax). The order of operations for a query depends only
 // on its position, never on how the tokens were cut into steps or batched. `sinks` (float32
-// [heads] or null) adds exp(sink) of the query's head to the softmax's denominator.
+// [heads] or null) adds exp(sink) of the query's head to the softmax's denominator. With
+// `keep_first` the keys at positions below it stay visible behind a window: their blocks come
+// first, the blocks between them and the window's first are skipped.
 //
 // This kernel serves the 32-bit engine and every shape that the faster kernels refuse.
 #include "common.cuh"
@@ -24,7 +26,8 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ kv,
                          long long kv_half, const int* __restrict__ positions,
                          const int* __restrict__ token_request, T* __restrict__ out, int tokens,
                          int heads, int kv_heads, int head_dim, float scale, int window,
-                         const float* __restrict__ sinks, int* __restrict__ error_flag) {
+                         int keep_first, const float* __restrict__ sinks,
+                         int* __restrict__ error_flag) {
     extern __shared__ float shared[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * WARPS + warp;
@@ -51,9 +54,12 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ kv,
     for (int i = 0; i < MAX_ACC; ++i) acc[i] = 0.f;
     const int pieces = (head_dim + 31) / 32;
 
-    for (int base = (lowest / 32) * 32; base <= position; base += 32) {
+    const int kept = min(keep_first, lowest);          // keys below this stay visible
+    const int window_base = (lowest / 32) * 32;
+    for (int base = kept > 0 ? 0 : window_base; base <= position; base += 32) {
+        if (base >= kept && base < window_base) { base = window_base - 32; continue; }
         const int key = base + lane;
-        const bool live = key >= lowest && key <= position;
+        const bool live = (key >= lowest || key < kept) && key <= position;
         float score = -INFINITY;
         const T* key_row = nullptr;
         if (live) {
@@ -104,15 +110,12 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ kv,
 
 }  // namespace
 
-// `planes`: 2 = values lie in a second plane behind all keys' pages; 1 = a token's row is its key
-// and its value.
-MLXONE_API int mlxone_attention_generic_planes(const void* q, const void* kv,
-                                               const int* block_table, int table_width,
-                                               int page_size, int pages, const int* positions,
-                                               const int* token_request, void* out, int tokens,
-                                               int heads, int kv_heads, int head_dim, float scale,
-                                               int window, int dtype, const float* sinks,
-                                               int planes, int* error_flag, cudaStream_t stream) {
+static int attention_generic_launch(const void* q, const void* kv, const int* block_table,
+                                    int table_width, int page_size, int pages, const int* positions,
+                                    const int* token_request, void* out, int tokens, int heads,
+                                    int kv_heads, int head_dim, float scale, int window, int dtype,
+                                    const float* sinks, int planes, int* error_flag,
+                                    cudaStream_t stream, int keep_first) {
     if (tokens == 0) return 0;
     MLXONE_REQUIRE(tokens > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
                    "attention: %d heads cannot share %d key heads", heads, kv_heads);
@@ -128,17 +131,31 @@ MLXONE_API int mlxone_attention_generic_planes(const void* q, const void* kv,
         using T = __nv_bfloat16;
         attention_generic_kernel<T><<<blocks, WARPS * 32, shared, stream>>>(
             (const T*)q, (const T*)kv, block_table, table_width, page_size, kv_half, positions,
-            token_request, (T*)out, tokens, heads, kv_heads, head_dim, scale, window, sinks,
-            error_flag);
+            token_request, (T*)out, tokens, heads, kv_heads, head_dim, scale, window, keep_first,
+            sinks, error_flag);
     } else {
         using T = float;
         attention_generic_kernel<T><<<blocks, WARPS * 32, shared, stream>>>(
             (const T*)q, (const T*)kv, block_table, table_width, page_size, kv_half, positions,
-            token_request, (T*)out, tokens, heads, kv_heads, head_dim, scale, window, sinks,
-            error_flag);
+            token_request, (T*)out, tokens, heads, kv_heads, head_dim, scale, window, keep_first,
+            sinks, error_flag);
     }
     MLXONE_LAUNCH_CHECK("attention_generic");
     return 0;
+}
+
+// `planes`: 2 = values lie in a second plane behind all keys' pages; 1 = a token's row is its key
+// and its value.
+MLXONE_API int mlxone_attention_generic_planes(const void* q, const void* kv,
+                                               const int* block_table, int table_width,
+                                               int page_size, int pages, const int* positions,
+                                               const int* token_request, void* out, int tokens,
+                                               int heads, int kv_heads, int head_dim, float scale,
+                                               int window, int dtype, const float* sinks,
+                                               int planes, int* error_flag, cudaStream_t stream) {
+    return attention_generic_launch(q, kv, block_table, table_width, page_size, pages, positions,
+                                    token_request, out, tokens, heads, kv_heads, head_dim, scale,
+                                    window, dtype, sinks, planes, error_flag, stream, 0);
 }
 
 MLXONE_API int mlxone_attention_generic(const void* q, const void* kv, const int* block_table,
@@ -151,4 +168,19 @@ MLXONE_API int mlxone_attention_generic(const void* q, const void* kv, const int
                                            positions, token_request, out, tokens, heads, kv_heads,
                                            head_dim, scale, window, dtype, sinks, 2, error_flag,
                                            stream);
+}
+
+// ... with a window behind which the first `keep_first` positions stay visible
+MLXONE_API int mlxone_attention_generic_keep(const void* q, const void* kv, const int* block_table,
+                                             int table_width, int page_size, int pages,
+                                             const int* positions, const int* token_request,
+                                             void* out, int tokens, int heads, int kv_heads,
+                                             int head_dim, float scale, int window, int keep_first,
+                                             int dtype, const float* sinks, int* error_flag,
+                                             cudaStream_t stream) {
+    MLXONE_REQUIRE(keep_first >= 0 && (keep_first == 0 || window > 0),
+                   "attention: first positions are kept behind a window only");
+    return attention_generic_launch(q, kv, block_table, table_width, page_size, pages, positions,
+                                    token_request, out, tokens, heads, kv_heads, head_dim, scale,
+                                    window, dtype, sinks, 2, error_flag, stream, keep_first);
 }

@@ -170,6 +170,27 @@ differential_combine_kernel(const T* __restrict__ maps, T* __restrict__ out, lon
     }
 }
 
+// The heads' outputs times a sigmoid gate: values [tokens, heads, row_dim], of which the first
+// value_dim of a row count, -> out [tokens, heads * value_dim]; the gate has one number per value
+// (rows [heads * value_dim]) or, with `per_head`, one per head (rows [heads]); its rows may be a
+// slice of wider rows.
+template <typename T>
+__global__ void gate_heads_kernel(const T* __restrict__ values, const T* __restrict__ gate, int ld_gate,
+                                  T* __restrict__ out, int heads, int row_dim, int value_dim,
+                                  int per_head, long long total) {
+    griddep_launch();
+    griddep_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int width = heads * value_dim;
+    const long long t = i / width;
+    const int c = (int)(i - t * width);
+    const int head = c / value_dim, e = c - head * value_dim;
+    const float g = to_float<T>(gate[t * ld_gate + (per_head ? head : c)]);
+    const float v = to_float<T>(values[(t * heads + head) * row_dim + e]);
+    out[i] = from_float<T>(v / (1.f + expf(-g)));
+}
+
 }  // namespace
 
 MLXONE_API int mlxone_latent_prepare(const void* projected, int ld, void* queries,
@@ -254,5 +275,27 @@ MLXONE_API int mlxone_differential_combine(const void* maps, void* out, int toke
                       factor);
     }
     MLXONE_LAUNCH_CHECK("differential_combine");
+    return 0;
+}
+
+MLXONE_API int mlxone_gate_heads(const void* values, const void* gate, int ld_gate, void* out,
+                                 int tokens, int heads, int row_dim, int value_dim, int per_head,
+                                 int dtype, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    MLXONE_REQUIRE(heads > 0 && value_dim > 0 && value_dim <= row_dim,
+                   "gate_heads: values of %d in rows of %d", value_dim, row_dim);
+    const long long total = (long long)tokens * heads * value_dim;
+    if (dtype == MLXONE_BF16) {
+        using T = __nv_bfloat16;
+        launch_kernel(gate_heads_kernel<T>, dim3(ceil_div_host(total, 256)), dim3(256), 0, stream,
+                      true, (const T*)values, (const T*)gate, ld_gate, (T*)out, heads, row_dim,
+                      value_dim, per_head, total);
+    } else {
+        using T = float;
+        launch_kernel(gate_heads_kernel<T>, dim3(ceil_div_host(total, 256)), dim3(256), 0, stream,
+                      true, (const T*)values, (const T*)gate, ld_gate, (T*)out, heads, row_dim,
+                      value_dim, per_head, total);
+    }
+    MLXONE_LAUNCH_CHECK("gate_heads");
     return 0;
 }

@@ -93,6 +93,86 @@ route_experts_kernel(const T* __restrict__ x, int ld, const float* __restrict__ 
     }
 }
 
+// The second routing kernel: scores over all `outputs` of the router (sigmoid, or softmax over all
+// of them), an optional correction per output that is added where the `top` best are chosen
+// (ties: the lower index) and nowhere else, weights = the chosen outputs' scores, divided by their
+// sum only with `normalize`. The first `experts` outputs are experts with tensors: their weights
+// go to weights[t, experts]. The outputs behind them hand the token on as it is: the sum of their
+// chosen weights goes to others[0][t]. With `shared_gate` the router has one more row behind its
+// outputs, and others[1][t] = sigmoid of that row's product with the token.
+template <typename T>
+__global__ void __launch_bounds__(ROUTE_THREADS)
+route_general_kernel(const T* __restrict__ x, int ld, const float* __restrict__ router,
+                     const float* __restrict__ correction, float* __restrict__ weights,
+                     float* __restrict__ others, int tokens, int hidden, int experts, int outputs,
+                     int top, int softmax, int normalize, int shared_gate) {
+    __shared__ float score[MAX_EXPERTS + 1];
+    __shared__ float choice[MAX_EXPERTS];
+    griddep_launch();
+    griddep_wait();
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const T* row = x + (size_t)t * ld;
+    const int rows = outputs + (shared_gate ? 1 : 0);
+    for (int e = warp; e < rows; e += ROUTE_THREADS / 32) {
+        const float* w = router + (size_t)e * hidden;
+        float sum = 0.f;
+        for (int c = lane; c < hidden; c += 32) sum = fmaf(to_float<T>(row[c]), w[c], sum);
+        sum = warp_sum(sum);
+        if (lane == 0) score[e] = sum;
+    }
+    for (int e = threadIdx.x; e < experts; e += ROUTE_THREADS)
+        weights[(size_t)t * experts + e] = 0.f;
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    if (softmax) {
+        float most = -INFINITY, total = 0.f;
+        for (int e = 0; e < outputs; ++e) most = fmaxf(most, score[e]);
+        for (int e = 0; e < outputs; ++e) { score[e] = expf(score[e] - most); total += score[e]; }
+        for (int e = 0; e < outputs; ++e) score[e] /= total;
+    } else {
+        for (int e = 0; e < outputs; ++e) score[e] = 1.f / (1.f + expf(-score[e]));
+    }
+    for (int e = 0; e < outputs; ++e)
+        choice[e] = correction != nullptr ? score[e] + correction[e] : score[e];
+    int chosen[64];
+    int count = 0;
+    float total = 0.f;
+    for (int pick = 0; pick < top; ++pick) {
+        int best = -1;
+        float best_value = -INFINITY;
+        for (int e = 0; e < outputs; ++e)
+            if (choice[e] > best_value) { best_value = choice[e]; best = e; }
+        if (best < 0) break;
+        choice[best] = -INFINITY;
+        chosen[count++] = best;
+        total += score[best];
+    }
+    const float factor = normalize ? 1.f / (total + 1e-20f) : 1.f;
+    float handed_on = 0.f;
+    // (in ascending order of the outputs, so that the sum does not depend on the ranking)
+    for (int e = experts; e < outputs; ++e)
+        for (int i = 0; i < count; ++i)
+            if (chosen[i] == e) handed_on += score[e] * factor;
+    for (int i = 0; i < count; ++i)
+        if (chosen[i] < experts) weights[(size_t)t * experts + chosen[i]] = score[chosen[i]] * factor;
+    others[t] = handed_on;
+    others[(size_t)tokens + t] = shared_gate ? 1.f / (1.f + expf(-score[outputs])) : 1.f;
+}
+
+// out[t, c] += factors[t] * x[t, c], taken in 32-bit
+template <typename T>
+__global__ void add_scaled_rows_kernel(T* __restrict__ out, const T* __restrict__ x, int ld,
+                                       const float* __restrict__ factors, int hidden, long long total) {
+    griddep_launch();
+    griddep_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long long t = i / hidden;
+    const int c = (int)(i - t * hidden);
+    out[i] = from_float<T>(fmaf(factors[t], to_float<T>(x[t * ld + c]), to_float<T>(out[i])));
+}
+
 // x[t, e * width + f] *= weights[t, e] for e < experts (columns beyond experts * width stay).
 template <typename T>
 __global__ void scale_expert_columns_kernel(T* __restrict__ x, int ld, const float* __restrict__ weights,
@@ -324,5 +404,43 @@ MLXONE_API int mlxone_scale_expert_columns(void* x, int ld, const float* weights
         launch_kernel(scale_expert_columns_kernel<float>, dim3(blocks), dim3(256), 0, stream, true,
                       (float*)x, ld, weights, experts, width, total);
     MLXONE_LAUNCH_CHECK("scale_expert_columns");
+    return 0;
+}
+
+MLXONE_API int mlxone_route_general(const void* x, int ld, const float* router,
+                                    const float* correction, float* weights, float* others,
+                                    int tokens, int hidden, int experts, int identity, int top,
+                                    int softmax, int normalize, int shared_gate, int dtype,
+                                    cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    const int outputs = experts + identity;
+    MLXONE_REQUIRE(tokens > 0 && hidden > 0 && experts > 0 && identity >= 0 && outputs <= MAX_EXPERTS,
+                   "route_general: 1 to %d outputs of the router", MAX_EXPERTS);
+    MLXONE_REQUIRE(top > 0 && top <= 64 && top <= outputs, "route_general: top %d of %d outputs", top,
+                   outputs);
+    if (dtype == MLXONE_BF16)
+        launch_kernel(route_general_kernel<__nv_bfloat16>, dim3(tokens), dim3(ROUTE_THREADS), 0,
+                      stream, true, (const __nv_bfloat16*)x, ld, router, correction, weights, others,
+                      tokens, hidden, experts, outputs, top, softmax, normalize, shared_gate);
+    else
+        launch_kernel(route_general_kernel<float>, dim3(tokens), dim3(ROUTE_THREADS), 0, stream, true,
+                      (const float*)x, ld, router, correction, weights, others, tokens, hidden,
+                      experts, outputs, top, softmax, normalize, shared_gate);
+    MLXONE_LAUNCH_CHECK("route_general");
+    return 0;
+}
+
+MLXONE_API int mlxone_add_scaled_rows(void* out, const void* x, int ld, const float* factors,
+                                      int tokens, int hidden, int dtype, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    const long long total = (long long)tokens * hidden;
+    if (dtype == MLXONE_BF16)
+        launch_kernel(add_scaled_rows_kernel<__nv_bfloat16>, dim3(ceil_div_host(total, 256)),
+                      dim3(256), 0, stream, true, (__nv_bfloat16*)out, (const __nv_bfloat16*)x, ld,
+                      factors, hidden, total);
+    else
+        launch_kernel(add_scaled_rows_kernel<float>, dim3(ceil_div_host(total, 256)), dim3(256), 0,
+                      stream, true, (float*)out, (const float*)x, ld, factors, hidden, total);
+    MLXONE_LAUNCH_CHECK("add_scaled_rows");
     return 0;
 }

@@ -108,6 +108,23 @@ MLXONE_API int mlxone_softcap(float* x, long long total, float cap, cudaStream_t
     return 0;
 }
 
+// ------------------------------------------------------------------ a factor on 32-bit values
+__global__ void scale_values_kernel(float* __restrict__ x, long long total, float factor) {
+    griddep_launch();
+    griddep_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) x[i] *= factor;
+}
+
+MLXONE_API int mlxone_scale_values(float* x, long long total, float factor, cudaStream_t stream) {
+    if (total == 0) return 0;
+    MLXONE_REQUIRE(total > 0, "scale_values: bad arguments");
+    launch_kernel(scale_values_kernel, dim3(ceil_div_host(total, 256)), dim3(256), 0, stream, true, x,
+                  total, factor);
+    MLXONE_LAUNCH_CHECK("scale_values");
+    return 0;
+}
+
 // ------------------------------------------------------------------ gate with any activation
 // out[t, f] = act(gate_up[t, f]) * gate_up[t, width + f], in 32-bit.
 template <typename T>

@@ -58,6 +58,7 @@ class CudaOps:
         self.lib.mlxone_gated_delta_scratch.restype = ctypes.c_longlong
         self.lib.mlxone_gated_delta_state.restype = ctypes.c_longlong
         self.lib.mlxone_lightning_scratch.restype = ctypes.c_longlong
+        self.lib.mlxone_state_space_scratch.restype = ctypes.c_longlong
         if self.lib.mlxone_abi_version() != 1:
             raise KernelBuildError("the CUDA extension is of another version; rebuild it")
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -756,6 +757,162 @@ class CudaOps:
                    _c_void_p(_ptr(weights)), _c_int(gated.shape[0]), _c_int(weights.shape[1]),
                    _c_int(width), _c_int(_dtype_code(gated.dtype)))
 
+    def route_general(self, x, router, correction, *, experts, identity, top, scores, normalize,
+                      shared_gate):
+        """The second routing kernel. ``router`` float32 [experts + identity (+ 1 with
+        ``shared_gate``), hidden]; scores are the sigmoid of the 32-bit logits or their softmax
+        over the experts + identity outputs; ``correction`` (float32 per output, or None) is
+        added where the ``top`` best are chosen; the weights are the chosen scores, divided by
+        their sum with ``normalize``. Returns (weights float32 [tokens, experts], zero where an
+        expert was not chosen; others float32 [2, tokens]: the sum of the chosen identity
+        outputs' weights, and the sigmoid of the router's last row's logit, 1 without
+        ``shared_gate``)."""
+        self._need_rows(x, x.dtype, "x")
+        self._need(router, torch.float32, "router")
+        rows = experts + identity + (1 if shared_gate else 0)
+        if router.shape != (rows, x.shape[1]):
+            raise KernelError("the router's shape does not match")
+        if scores not in ("sigmoid", "softmax"):
+            raise KernelError(f"unknown routing scores {scores!r}")
+        if correction is not None:
+            self._need(correction, torch.float32, "correction")
+            if correction.numel() != experts + identity:
+                raise KernelError("one correction per output of the router")
+        tokens = x.shape[0]
+        weights = torch.empty((tokens, experts), dtype=torch.float32, device=self.device)
+        others = torch.empty((2, tokens), dtype=torch.float32, device=self.device)
+        self._call("mlxone_route_general", _c_void_p(_ptr(x)), _c_int(x.stride(0)),
+                   _c_void_p(_ptr(router)), _c_void_p(_ptr(correction)), _c_void_p(_ptr(weights)),
+                   _c_void_p(_ptr(others)), _c_int(tokens), _c_int(x.shape[1]), _c_int(experts),
+                   _c_int(identity), _c_int(top), _c_int(1 if scores == "softmax" else 0),
+                   _c_int(1 if normalize else 0), _c_int(1 if shared_gate else 0),
+                   _c_int(_dtype_code(x.dtype)))
+        return weights, others
+
+    def add_scaled_rows(self, out, x, factors):
+        """In place: out[t] += factors[t] * x[t] (32-bit sum, stored in out's dtype)."""
+        self._need(out, out.dtype, "out")
+        self._need_rows(x, out.dtype, "x")
+        self._need(factors, torch.float32, "factors")
+        if x.shape != out.shape or factors.numel() != out.shape[0]:
+            raise KernelError("rows, their source and one factor per row must match")
+        self._call("mlxone_add_scaled_rows", _c_void_p(_ptr(out)), _c_void_p(_ptr(x)),
+                   _c_int(x.stride(0)), _c_void_p(_ptr(factors)), _c_int(out.shape[0]),
+                   _c_int(out.shape[1]), _c_int(_dtype_code(out.dtype)))
+
+    def scale_values(self, values, factor):
+        """In place: values *= factor (float32)."""
+        self._need(values, torch.float32, "values")
+        self._call("mlxone_scale_values", _c_void_p(_ptr(values)), _c_ll(values.numel()),
+                   _c_float(factor))
+
+    # ---- convolutions over time on the channels of a projection; the selective state space
+
+    def channel_conv(self, rows, kernel, bias, *, taps, activation, ctx, view, write):
+        """act(sum_j kernel[:, j] * rows_(t - taps + 1 + j) + bias) over each request's tokens;
+        the taps - 1 rows before a step's first token come from the request's slot (``view``:
+        [slots, taps - 1, channels] in the rows' dtype), where the step's last rows are left.
+        ``rows`` may be a slice of wider rows; the result has rows of its own. ``activation``:
+        None or ``silu``. A step of single tokens is one kernel, else the convolution and the
+        slots' update."""
+        self._need_rows(rows, rows.dtype, "rows")
+        tokens, channels = rows.shape
+        self._need(kernel, torch.float32, "conv kernel")
+        if kernel.shape != (channels, taps):
+            raise KernelError("the convolution's weights are [channels, taps]")
+        if bias is not None:
+            self._need(bias, torch.float32, "conv bias")
+        if activation not in (None, "silu"):
+            raise KernelError(f"unknown activation {activation!r}")
+        state = slots = None
+        if taps > 1:
+            self._need(view.state, rows.dtype, "state")
+            if view.state.shape[1:] != (taps - 1, channels):
+                raise KernelError("a slot keeps taps - 1 rows of the convolution's inputs")
+            state, slots = view.state, view.slots
+        out = torch.empty((tokens, channels), dtype=rows.dtype, device=self.device)
+        single = ctx.max_portion == 1 and tokens == ctx.requests
+        self._call("mlxone_channel_conv", _c_void_p(_ptr(rows)), _c_int(rows.stride(0)),
+                   _c_void_p(_ptr(kernel)), _c_void_p(_ptr(bias)), _c_void_p(_ptr(state)),
+                   _c_void_p(_ptr(slots)), _c_void_p(_ptr(ctx.token_request)),
+                   _c_void_p(_ptr(ctx.request_start)), _c_void_p(_ptr(ctx.history)),
+                   _c_void_p(_ptr(out)), _c_int(tokens), _c_int(ctx.requests), _c_int(channels),
+                   _c_int(taps), _c_int(1 if activation == "silu" else 0),
+                   _c_int(1 if single else 0), _c_int(1 if write else 0),
+                   _c_int(_dtype_code(rows.dtype)))
+        if not single and write and taps > 1:
+            self.launches += 1
+        return out
+
+    def state_space_scan(self, mixed, steps, *, a_log, dt_bias, skip, ctx, view, write, heads,
+                         value_dim, state_dim, groups):
+        """The recurrence of a selective state space. ``mixed`` [tokens, x | B | C] (heads *
+        value_dim, then twice groups * state_dim) and ``steps`` [tokens, heads] (raw step sizes,
+        may be a slice of wider rows) in the compute dtype; dt = softplus(steps + dt_bias),
+        S = exp(-exp(a_log) dt) S + dt B x^T, y = S^T C + skip x over each request's tokens on
+        its 32-bit state [heads, state_dim, value_dim]. Returns y float32 [tokens, heads *
+        value_dim]."""
+        tokens = mixed.shape[0]
+        self._need(mixed, mixed.dtype, "mixed")
+        self._need_rows(steps, mixed.dtype, "steps")
+        inner = heads * value_dim
+        if mixed.shape[1] != inner + 2 * groups * state_dim or steps.shape != (tokens, heads):
+            raise KernelError("the convolution's width does not match the head counts")
+        for tensor, what in ((a_log, "A_log"), (dt_bias, "dt_bias"), (skip, "D"),
+                             (view.state, "state")):
+            self._need(tensor, torch.float32, what)
+        if view.state[0].numel() != heads * state_dim * value_dim:
+            raise KernelError(f"a state slot has {view.state[0].numel()} values, the mixer needs "
+                              f"{heads * state_dim * value_dim}")
+        scratch = torch.empty(self.lib.mlxone_state_space_scratch(
+            tokens, ctx.requests, ctx.max_portion, heads, value_dim, state_dim),
+            dtype=torch.float32, device=self.device)
+        y = torch.empty((tokens, inner), dtype=torch.float32, device=self.device)
+        self._call("mlxone_state_space_scan", _c_void_p(_ptr(mixed)), _c_void_p(_ptr(steps)),
+                   _c_int(steps.stride(0)), _c_void_p(_ptr(a_log)), _c_void_p(_ptr(dt_bias)),
+                   _c_void_p(_ptr(skip)), _c_void_p(_ptr(view.state)), _c_void_p(_ptr(view.slots)),
+                   _c_void_p(_ptr(ctx.request_start)), _c_void_p(_ptr(scratch)),
+                   _c_void_p(_ptr(y)), _c_int(tokens), _c_int(ctx.requests),
+                   _c_int(ctx.max_portion), _c_int(heads), _c_int(value_dim), _c_int(state_dim),
+                   _c_int(groups), _c_int(1 if write else 0), _c_int(_dtype_code(mixed.dtype)))
+        if ctx.max_portion >= 128:
+            self.launches += 2
+        return y
+
+    def gated_group_norm(self, y, gate, weight, *, groups, eps, dtype):
+        """(y * silu(gate)) divided by its root mean square in ``groups`` equal parts of a row
+        (each part by its own), times ``weight``; y float32 [tokens, inner], the gate's rows in
+        ``dtype`` (may be a slice of wider rows); the result in ``dtype``."""
+        self._need(y, torch.float32, "y")
+        self._need_rows(gate, dtype, "gate")
+        self._need(weight, torch.float32, "norm weight")
+        tokens, inner = y.shape
+        if gate.shape != y.shape or weight.numel() != inner or inner % groups:
+            raise KernelError("gate, weight and the norm's parts must match the rows")
+        out = torch.empty((tokens, inner), dtype=dtype, device=self.device)
+        self._call("mlxone_gated_group_norm", _c_void_p(_ptr(y)), _c_void_p(_ptr(gate)),
+                   _c_int(gate.stride(0)), _c_void_p(_ptr(weight)), _c_void_p(_ptr(out)),
+                   _c_int(tokens), _c_int(inner), _c_int(groups), _c_float(eps),
+                   _c_int(_dtype_code(dtype)))
+        return out
+
+    def gate_heads(self, mixed, gate, *, heads, row_dim, value_dim, per_head):
+        """The heads' outputs [tokens, heads * row_dim] (the first ``value_dim`` values of a
+        head's row count) times sigmoid(gate), one number per value or, with ``per_head``, per
+        head -> [tokens, heads * value_dim]. The gate's rows may be a slice of wider rows."""
+        self._need(mixed, mixed.dtype, "mixed")
+        self._need_rows(gate, mixed.dtype, "gate")
+        tokens = mixed.shape[0]
+        if mixed.shape[1] != heads * row_dim or \
+                gate.shape != (tokens, heads * (1 if per_head else value_dim)):
+            raise KernelError("the gate does not match the heads' outputs")
+        out = torch.empty((tokens, heads * value_dim), dtype=mixed.dtype, device=self.device)
+        self._call("mlxone_gate_heads", _c_void_p(_ptr(mixed)), _c_void_p(_ptr(gate)),
+                   _c_int(gate.stride(0)), _c_void_p(_ptr(out)), _c_int(tokens), _c_int(heads),
+                   _c_int(row_dim), _c_int(value_dim), _c_int(1 if per_head else 0),
+                   _c_int(_dtype_code(mixed.dtype)))
+        return out
+
     # Steps of at least this many tokens run routed experts over tokens sorted by expert (grouped
     # tcgen05 products that touch only the experts a token uses), and so do steps so small that
     # their tokens use at most half of the experts (a single token that uses 2 of 8, or 6 of 64,
@@ -772,7 +929,7 @@ class CudaOps:
                 and x.stride(1) == 1 and x.stride(0) % 8 == 0)
 
     def routed_experts_sorted(self, x, weights, gate_up, down, *, experts, width, top,
-                              shared_gate_up=None, shared_down=None):
+                              shared_gate_up=None, shared_down=None, shared_scale=None):
         """The weighted sum of every token's chosen experts (+ the shared expert's output), with
         the tokens sorted by expert: gate_up [2 stack, hidden] holds the experts' gate rows, then
         (``stack`` rows further) their up rows; down [hidden, stack] their down matrices side by
@@ -806,7 +963,13 @@ class CudaOps:
                    _c_void_p(_ptr(self.error_flag)))
         shared_out = None
         if shared_gate_up is not None:
-            shared_out = self.linear(self.linear_swiglu(x, shared_gate_up), shared_down)
+            shared_gated = self.linear_swiglu(x, shared_gate_up)
+            if shared_scale is not None:
+                # (one number per token on the shared expert's output, applied ahead of its down
+                # product, which is linear)
+                self.scale_expert_columns(shared_gated, shared_scale.view(-1, 1),
+                                          shared_gated.shape[1])
+            shared_out = self.linear(shared_gated, shared_down)
         out = torch.empty((tokens, hidden), dtype=x.dtype, device=self.device)
         self._call("mlxone_combine_experts", _c_void_p(_ptr(y)), _c_void_p(_ptr(pair_row)),
                    _c_void_p(_ptr(weights)), _c_void_p(_ptr(shared_out)), _c_void_p(_ptr(out)),
@@ -1031,7 +1194,8 @@ class CudaOps:
         return -int(chunk) if chunk else int(window or 0)
 
     def qkv_attention(self, qkv, *, heads, kv_heads, head_dim, q_weight, k_weight, eps, rotary,
-                      scale, window, ctx, view, write, sinks=None, chunk=None, **extra):
+                      scale, window, ctx, view, write, sinks=None, chunk=None, keep_first=0,
+                      **extra):
         """From the fused projection qkv [tokens, (heads + 2 kv_heads) * head_dim] to the mixed
         heads [tokens, heads * head_dim]: per-head norm of queries and keys, rotation, keys and
         values appended to the pages, attention. A step of single tokens in bfloat16 whose head
@@ -1049,10 +1213,10 @@ class CudaOps:
                                         rotary=rotary, ctx=ctx, view=view, write=write, **extra)
             return self.paged_attention(q, heads=heads, kv_heads=kv_heads,
                                         head_dim=view.kv.shape[-1], scale=scale, window=window,
-                                        ctx=ctx, view=view, sinks=sinks)
+                                        ctx=ctx, view=view, sinks=sinks, keep_first=keep_first)
         if (self.fused_decode_attention and qkv.dtype == torch.bfloat16
                 and ctx.max_portion == 1 and tokens == ctx.requests
-                and self.tensor_core_attention
+                and self.tensor_core_attention and not keep_first
                 and self.lib.mlxone_attention_decode_fused_supports(_c_int(head_dim))
                 and (inv_freq is None or rotary_dim == head_dim)
                 and (q_weight is None) == (k_weight is None)):
@@ -1080,11 +1244,13 @@ class CudaOps:
                                     q_weight=q_weight, k_weight=k_weight, eps=eps, rotary=rotary,
                                     ctx=ctx, view=view, write=write)
         return self.paged_attention(q, heads=heads, kv_heads=kv_heads, head_dim=head_dim,
-                                    scale=scale, window=window, ctx=ctx, view=view, sinks=sinks)
+                                    scale=scale, window=window, ctx=ctx, view=view, sinks=sinks,
+                                    keep_first=keep_first)
 
     def paged_attention(self, q, *, heads, kv_heads, head_dim, scale, window, ctx, view,
-                        sinks=None, chunk=None):
-        """Attention of every token over its request's pages. bfloat16 with a head size that
+                        sinks=None, chunk=None, keep_first=0):
+        """Attention of every token over its request's pages. ``keep_first``: behind a window the
+        first ``keep_first`` positions of a sequence stay visible. bfloat16 with a head size that
         is a multiple of 16 up to 128 runs on tensor cores: the split-key decode kernel when
         every request brings one token, else the prefill kernel. Everything else (float32,
         other head sizes) runs the general kernel."""
@@ -1101,6 +1267,16 @@ class CudaOps:
             self._need(sinks, torch.float32, "sinks")
             if sinks.numel() != heads:
                 raise KernelError("one sink per query head")
+        keep_first = int(keep_first or 0) if window > 0 else 0
+        if keep_first:
+            self._call("mlxone_attention_generic_keep", _c_void_p(_ptr(q)), _c_void_p(_ptr(view.kv)),
+                       _c_void_p(_ptr(view.block_table)), _c_int(width), _c_int(view.page_size),
+                       _c_int(pages), _c_void_p(_ptr(ctx.positions)),
+                       _c_void_p(_ptr(ctx.token_request)), _c_void_p(_ptr(out)), _c_int(tokens),
+                       _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_float(scale),
+                       _c_int(window), _c_int(keep_first), _c_int(code), _c_void_p(_ptr(sinks)),
+                       _c_void_p(_ptr(self.error_flag)))
+            return out
         if self.tensor_core_attention and self.lib.mlxone_attention_mma_supports(head_dim, code):
             if ctx.max_portion == 1 and tokens == ctx.requests:
                 self._decode_attention(q, out, ctx.requests, heads, kv_heads, head_dim, scale,

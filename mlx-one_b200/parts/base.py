@@ -20,13 +20,16 @@ class PagedKeyValues:
     ``window`` positions are ever read again, so earlier pages may be given back. ``chunk``:
     a query reads only keys of its own chunk of ``chunk`` positions (counted from 0), so the
     pages of chunks that have ended may be given back. ``planes``: 2 for keys and values; 1 for
-    a mixer that keeps one row per token and reads it as key and as value."""
+    a mixer that keeps one row per token and reads it as key and as value. ``keep_first``: with a
+    window, the sequence's first ``keep_first`` positions are read by every later query, so the
+    pages that hold them are never given back."""
 
     kv_heads: int
     head_dim: int
     window: int | None = None
     chunk: int | None = None
     planes: int = 2
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)

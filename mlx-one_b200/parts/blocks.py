@@ -120,3 +120,48 @@ class OutputNormBlock(Block):
             raise ValueError(f"call {place} of the order averages {place + 2} streams, "
                              f"{self.average.numel()} weights are stored")
         return self.ops.stream_average(kept, self.average, place + 2, kept[place + 2]), None
+
+
+@BLOCKS.register("sandwich")
+class SandwichBlock(Block):
+    """x <- x + post1(mixer(norm1(x))); x <- x + post2(feed_forward(norm2(x))): every part reads
+    the normed stream and its output is normed once more before it is added. The norms ahead of
+    the parts are the layer's ``mixer_norm`` and ``feed_forward_norm``; the norms behind them are
+    the block's own: v / rms(v) * (offset + weight) over the model width, with the stored weights
+    ``post_mixer`` and ``post_feed_forward``, taken and added in 32-bit. A layer without a
+    feed-forward ends after the mixer. Parameters: ``size``, ``eps``, ``offset`` (0; 1 for
+    weights stored around zero), ``feed_forward`` (True: the layer has one)."""
+
+    @classmethod
+    def tensors(cls, spec):
+        init = "norm0" if spec.get("offset") else "norm"
+        out = {"post_mixer": TensorSpec((spec["size"],), init)}
+        if spec.get("feed_forward", True):
+            out["post_feed_forward"] = TensorSpec((spec["size"],), init)
+        return out
+
+    def __init__(self, spec, tensors, runtime, **roles):
+        super().__init__(spec, tensors, runtime, **roles)
+        self.eps = float(spec["eps"])
+        offset = float(spec.get("offset") or 0.0)
+        weight = lambda name: (self.vector(tensors[name]) + offset).contiguous()
+        self.post_mixer = weight("post_mixer")
+        self.post_feed_forward = weight("post_feed_forward") if "post_feed_forward" in tensors else None
+        if (self.feed_forward is None) != (self.post_feed_forward is None):
+            raise ValueError("a feed-forward and the norm behind it come together")
+
+    def _read(self, norm, residual, delta, consumer, scale=1.0):
+        extra = {} if scale == 1.0 else {"delta_scale": scale}
+        if delta is None and consumer.accepts_normed_input and norm.supports_lazy:
+            return norm.forward(residual, delta, lazy=True, **extra)
+        return norm.forward(residual, delta, **extra)
+
+    def forward(self, residual, delta, ctx, cache, write, delta_scale=1.0):
+        normed = self._read(self.mixer_norm, residual, delta, self.mixer, delta_scale)
+        mixed = self.mixer.forward(normed, ctx, cache, write)
+        self.ops.normed_mean_add(residual, [mixed], [self.post_mixer], self.eps)
+        if self.feed_forward is not None:
+            normed = self._read(self.feed_forward_norm, residual, None, self.feed_forward)
+            out = self.feed_forward.forward(normed, ctx)
+            self.ops.normed_mean_add(residual, [out], [self.post_feed_forward], self.eps)
+        return None

@@ -97,12 +97,21 @@ class RoutedExperts(FeedForward):
     ``experts``, ``top`` (experts a token uses), ``groups`` and ``keep`` (experts form ``groups``
     equal runs of neighbours; a group's score is the sum of its ``group_score`` largest scores,
     and only experts of the ``keep`` best groups can be chosen), ``shared_width`` (None: no
-    shared expert), ``activation`` of the gates, ``scores`` (``sigmoid``).
+    shared expert), ``activation`` of the gates, ``scores`` (``sigmoid``, or ``softmax`` over all
+    outputs of the router), ``correction`` (True: the stored ``correction``, one number per
+    output of the router, is added to the scores where experts are chosen, and only there),
+    ``normalize`` (True; False: the chosen experts keep their scores as weights), ``identity``
+    (0: that many further outputs of the router, behind the experts', stand for experts without
+    tensors whose output is the input itself), ``shared_gate`` (True: the shared expert's output
+    is multiplied by sigmoid(w x), one number per token, with the stored ``shared.sg`` [1,
+    hidden]).
 
     Router logits W_r x are 32-bit, scores s = sigmoid of them; the ``top`` allowed experts
     with the largest scores are chosen and weighted with s / (sum of the chosen s + 1e-20). The
     output is the weighted sum of the chosen experts' down(act(gate x) * up x), plus the shared
-    expert's, which every token uses with weight 1.
+    expert's, which every token uses with weight 1. The options above (softmax scores, a
+    correction, weights that are not normalised, identity outputs, a gated shared expert) go
+    through a second routing kernel that has no groups.
 
     The experts' gate and up matrices are stacked into one matrix and their down matrices side
     by side into another (the shared expert last). Small steps run every token through all of
@@ -115,7 +124,14 @@ class RoutedExperts(FeedForward):
     @classmethod
     def tensors(cls, spec):
         hidden, width = spec["hidden"], spec["width"]
-        out = {"router": TensorSpec((spec["experts"], hidden), "wide")}
+        outputs = spec["experts"] + int(spec.get("identity") or 0)
+        out = {"router": TensorSpec((outputs, hidden), "wide")}
+        if spec.get("correction"):
+            out["correction"] = TensorSpec((outputs,), "norm0")
+        if spec.get("shared_gate"):
+            if not spec.get("shared_width"):
+                raise ValueError("a gate of the shared expert needs a shared expert")
+            out["shared.sg"] = TensorSpec((1, hidden), "wide")
         for e in range(spec["experts"]):
             out[f"e{e}.gate"] = TensorSpec((width, hidden))
             out[f"e{e}.up"] = TensorSpec((width, hidden))
@@ -132,17 +148,38 @@ class RoutedExperts(FeedForward):
         self.experts, self.width = spec["experts"], spec["width"]
         self.shared_width = spec.get("shared_width") or 0
         self.activation = spec.get("activation") or "silu"
-        if (spec.get("scores") or "sigmoid") != "sigmoid":
-            raise ValueError("routing scores other than sigmoid are not built")
+        scores = spec.get("scores") or "sigmoid"
+        if scores not in ("sigmoid", "softmax"):
+            raise ValueError(f"unknown routing scores {scores!r}")
+        self.identity = int(spec.get("identity") or 0)
+        self.shared_gate = bool(spec.get("shared_gate"))
+        normalize = spec.get("normalize", True)
         self.routing = dict(experts=self.experts, top=spec["top"], groups=spec.get("groups") or 1,
                             keep=spec.get("keep") or 1, group_score=spec.get("group_score") or 2)
         if self.experts % self.routing["groups"]:
             raise ValueError("experts must form equal groups")
+        # what the first routing kernel does not know goes to the second one
+        self.general = None
+        if (scores != "sigmoid" or spec.get("correction") or not normalize or self.identity
+                or self.shared_gate):
+            if self.routing["groups"] != 1:
+                raise ValueError("groups of experts go with sigmoid scores, normalised weights "
+                                 "and no identity outputs")
+            self.general = dict(experts=self.experts, identity=self.identity, top=spec["top"],
+                                scores=scores, normalize=bool(normalize),
+                                shared_gate=self.shared_gate)
+            self.correction = None
+            if spec.get("correction"):
+                self.correction = tensors["correction"].to(torch.float32).contiguous()
         names = [f"e{e}." for e in range(self.experts)] + (["shared."] if self.shared_width else [])
         self.gate_up = self.matrix(torch.cat([tensors[name + "gate"] for name in names] +
                                              [tensors[name + "up"] for name in names], dim=0))
         self.down = self.matrix(torch.cat([tensors[name + "down"] for name in names], dim=1))
         self.router = tensors["router"].to(torch.float32).contiguous()
+        if self.shared_gate:
+            # the gate's row behind the router's: one pass over the token serves both
+            self.router = torch.cat([self.router, tensors["shared.sg"].to(torch.float32)
+                                     .reshape(1, -1)], dim=0).contiguous()
         # the shared expert once more on its own, for steps that sort their tokens by expert
         self.shared = {}
         self.sortable = (self.activation == "silu" and hasattr(self.ops, "sorts_experts")
@@ -155,7 +192,36 @@ class RoutedExperts(FeedForward):
     fuses_residual = True
     scales_residual = True
 
+    def _forward_general(self, x, ctx):
+        """Routing with the second kernel: weights [tokens, experts] of the experts that have
+        tensors, and per token the sum of the chosen identity outputs' weights and the shared
+        expert's gate."""
+        weights, others = self.ops.route_general(x, self.router, self.correction, **self.general)
+        shared_scale = others[1] if self.shared_gate else None
+        if self.sortable and self.ops.sorts_experts(x, experts=self.experts, width=self.width,
+                                                    top=self.routing["top"],
+                                                    stack=self.gate_up.shape[0] // 2):
+            out = self.ops.routed_experts_sorted(
+                x, weights, self.gate_up, self.down, experts=self.experts, width=self.width,
+                top=self.routing["top"], shared_scale=shared_scale, **self.shared)
+        else:
+            if self.activation == "silu":
+                gated = self.ops.linear_swiglu(x, self.gate_up)
+            else:
+                gated = self.ops.linear_gated(x, self.gate_up, self.activation)
+            self.ops.scale_expert_columns(gated, weights, self.width)
+            if shared_scale is not None:
+                self.ops.scale_expert_columns(gated[:, self.experts * self.width:],
+                                              shared_scale.view(-1, 1), self.shared_width)
+            out = self.ops.linear(gated, self.down)
+        if self.identity:
+            self.ops.add_scaled_rows(out, x, others[0])
+        return out
+
     def forward(self, x, ctx, residual=None):
+        if self.general is not None:
+            out = self._forward_general(x, ctx)
+            return out          # (the caller adds it, with its factor, where it norms next)
         weights = self.ops.route_experts(x, self.router, **self.routing)
         if self.sortable and self.ops.sorts_experts(x, experts=self.experts, width=self.width,
                                                     top=self.routing["top"],

@@ -22,7 +22,17 @@ class Attention(Mixer):
     ``position`` (a position-encoding PartSpec), ``window`` (None = all keys), ``scale`` (None =
     head_dim^-0.5), ``sink`` (a stored number per query head, ``sink`` [heads], that stands in
     the softmax's denominator as exp(sink) beside the keys' terms: it has no key and no value
-    and is not scaled).
+    and is not scaled), ``keep_first`` (with a window: the sequence's first ``keep_first``
+    positions stay visible to every later query, at their true positions), ``values``
+    (``projected``, the default, or ``keys``: the values are the keys as projected, before norm
+    and rotation, and there is no value matrix; a bias then belongs to queries and keys),
+    ``conv_taps`` (None: none; else queries, keys and values pass, right after their projection,
+    a causal convolution over the last ``conv_taps`` tokens of their request on every channel,
+    with the stored ``q_conv``, ``k_conv``, ``v_conv`` [channels, taps], last column the current
+    token's; the last taps - 1 projected rows of a request are kept in a state slot), ``gate``
+    (None; ``values``: the heads' outputs are multiplied value by value with sigmoid(W_g x),
+    ``gate.weight`` [heads * value_dim, hidden]; ``heads``: one number per head, ``gate.weight``
+    [heads, hidden]; the gate reads the mixer's input and is applied before the output matrix).
 
     q, k, v projections (one fused matrix product), per-head RMSNorm of q and k, rotation,
     keys and values appended to the request's pages, causal softmax(q k^T scale) v where
@@ -53,16 +63,25 @@ class Attention(Mixer):
         hidden = spec["hidden"]
         hd, vd, _ = cls._sizes(spec)
         q_dim, k_dim, v_dim = spec["heads"] * hd, spec["kv_heads"] * hd, spec["kv_heads"] * vd
+        own_values = cls._own_values(spec)
         out = {
             "q_proj.weight": TensorSpec((q_dim, hidden)),
             "k_proj.weight": TensorSpec((k_dim, hidden)),
-            "v_proj.weight": TensorSpec((v_dim, hidden)),
             "out_proj.weight": TensorSpec((hidden, spec["heads"] * vd)),
         }
+        if own_values:
+            out["v_proj.weight"] = TensorSpec((v_dim, hidden))
         if spec.get("bias"):
             out["q_proj.bias"] = TensorSpec((q_dim,), "bias")
             out["k_proj.bias"] = TensorSpec((k_dim,), "bias")
-            out["v_proj.bias"] = TensorSpec((v_dim,), "bias")
+            if own_values:
+                out["v_proj.bias"] = TensorSpec((v_dim,), "bias")
+        if spec.get("conv_taps"):
+            for name, size in (("q_conv", q_dim), ("k_conv", k_dim), ("v_conv", v_dim)):
+                out[name] = TensorSpec((size, spec["conv_taps"]), "wide")
+        gate = cls._gate_kind(spec)
+        if gate is not None:
+            out["gate.weight"] = TensorSpec((spec["heads"] * (vd if gate == "values" else 1), hidden))
         if cls._norm_kind(spec) == "weighted_before":
             out["q_layernorm.weight"] = TensorSpec((hd,), "norm")
             out["k_layernorm.weight"] = TensorSpec((hd,), "norm")
@@ -70,9 +89,33 @@ class Attention(Mixer):
             out["sink"] = TensorSpec((spec["heads"],), "wide")
         return out
 
+    @staticmethod
+    def _own_values(spec):
+        kind = spec.get("values") or "projected"
+        if kind not in ("projected", "keys"):
+            raise ValueError(f"unknown values {kind!r}")
+        if kind == "keys" and (spec.get("value_dim") or spec["head_dim"]) != spec["head_dim"]:
+            raise ValueError("values that are the keys have the keys' size")
+        return kind == "projected"
+
+    @staticmethod
+    def _gate_kind(spec):
+        kind = spec.get("gate")
+        if kind not in (None, "values", "heads"):
+            raise ValueError(f"unknown gate {kind!r}")
+        return kind
+
     @classmethod
     def cache_need(cls, spec):
-        return PagedKeyValues(spec["kv_heads"], cls._sizes(spec)[2], spec.get("window"))
+        hd, vd, row = cls._sizes(spec)
+        window = spec.get("window")
+        pages = PagedKeyValues(spec["kv_heads"], row, window,
+                               keep_first=int(spec.get("keep_first") or 0) if window else 0)
+        taps = spec.get("conv_taps") or 0
+        if taps < 2:
+            return pages
+        channels = (spec["heads"] + spec["kv_heads"]) * hd + spec["kv_heads"] * vd
+        return {"pages": pages, "inputs": FixedState((taps - 1, channels))}
 
     def _reordered(self, weight, heads, order):
         """The rows of a projection [heads * head_dim, hidden] in another order within each
@@ -97,16 +140,42 @@ class Attention(Mixer):
         # of the query and key projections (and their biases) are put into that order once
         order = getattr(self.position, "row_order", lambda size: None)(self.head_dim)
         reorder = lambda name, heads: self._reordered(tensors[name], heads, order)
-        self.qkv = self.matrix(torch.cat([reorder("q_proj.weight", self.heads),
-                                          reorder("k_proj.weight", self.kv_heads),
-                                          tensors["v_proj.weight"]], dim=0))
-        self.qkv_bias = None
+        # values that are the keys as projected: the key matrix (in its stored order) once more
+        # in the values' place, so that everything behind the projection stays as it is
+        values = "v_proj" if self._own_values(spec) else "k_proj"
+        self.gate_kind = self._gate_kind(spec)
+        self.taps = int(spec.get("conv_taps") or 0)
+        self.keep_first = int(spec.get("keep_first") or 0) if self.window else 0
+        stacked = [reorder("q_proj.weight", self.heads), reorder("k_proj.weight", self.kv_heads),
+                   tensors[values + ".weight"]]
+        self.qkv_width = sum(weight.shape[0] for weight in stacked)
+        # The gate reads the same input: its rows follow those of q, k and v where what comes
+        # next takes a slice of wider rows (the convolution, the general preparation); the plain
+        # preparation kernels want rows of their own, and the gate is then a second product.
+        self.gate = None
+        biases = []
         if spec.get("bias"):
-            self.qkv_bias = self.vector(torch.cat([reorder("q_proj.bias", self.heads),
-                                                   reorder("k_proj.bias", self.kv_heads),
-                                                   tensors["v_proj.bias"]], dim=0))
+            biases = [reorder("q_proj.bias", self.heads), reorder("k_proj.bias", self.kv_heads),
+                      tensors[values + ".bias"]]
+        if self.gate_kind is not None:
+            general = (self.value_dim != self.head_dim or self._norm_kind(spec) == "plain_after"
+                       or self.position.amplitude() != 1.0)
+            if self.taps or general:
+                stacked.append(tensors["gate.weight"])
+                if biases:
+                    biases.append(torch.zeros(tensors["gate.weight"].shape[0],
+                                              dtype=biases[0].dtype, device=biases[0].device))
+            else:
+                self.gate = self.matrix(tensors["gate.weight"])
+        self.qkv = self.matrix(torch.cat(stacked, dim=0))
+        self.qkv_bias = self.vector(torch.cat(biases, dim=0)) if biases else None
+        self.conv = None
+        if self.taps:
+            self.conv = self.vector(torch.cat([reorder("q_conv", self.heads),
+                                               reorder("k_conv", self.kv_heads),
+                                               tensors["v_conv"]], dim=0))
         out = tensors["out_proj.weight"]
-        if self.value_dim < self.row_dim:
+        if self.value_dim < self.row_dim and self.gate_kind is None:
             # zero columns where the values' rows are padded
             wide = out.new_zeros((out.shape[0], self.heads, self.row_dim))
             wide[:, :, :self.value_dim] = out.view(out.shape[0], self.heads, self.value_dim)
@@ -132,6 +201,10 @@ class Attention(Mixer):
         self.sinks = {}
         if spec.get("sink"):
             self.sinks = dict(sinks=self.vector(tensors["sink"]))
+        if self.keep_first:
+            self.sinks["keep_first"] = self.keep_first
+        # (with a second product for the gate the input is read twice: it is normed once, ahead)
+        self.accepts_normed_input = self.gate is None
 
     fuses_residual = True
     scales_residual = True
@@ -142,18 +215,33 @@ class Attention(Mixer):
 
     def input_projection(self):
         # (the plain form's kernels want rows of their own, the general preparation takes slices)
-        return (self.qkv, self.qkv_bias) if self.extra else None
+        return (self.qkv, self.qkv_bias) if self.extra and self.gate is None else None
 
     def forward(self, x, ctx, cache, write, residual=None):
+        gate = None if self.gate is None else self.ops.linear(x, self.gate)
         return self.forward_projected(self.ops.linear(x, self.qkv, self.qkv_bias), ctx, cache,
-                                      write, residual)
+                                      write, residual, gate=gate)
 
-    def forward_projected(self, qkv, ctx, cache, write, residual=None):
+    def forward_projected(self, projected, ctx, cache, write, residual=None, gate=None):
+        qkv = projected if projected.shape[1] == self.qkv_width else projected[:, :self.qkv_width]
+        if self.gate_kind is not None and gate is None:
+            gate = projected[:, self.qkv_width:]
+        pages = cache
+        if self.taps:
+            pages = cache if self.taps < 2 else cache["pages"]
+            qkv = self.ops.channel_conv(qkv, self.conv, None, taps=self.taps, activation=None,
+                                        ctx=ctx, view=None if self.taps < 2 else cache["inputs"],
+                                        write=write)
         mixed = self.ops.qkv_attention(
             qkv, heads=self.heads, kv_heads=self.kv_heads, head_dim=self.head_dim,
             q_weight=self.q_norm, k_weight=self.k_norm, eps=self.eps,
             rotary=self.position.rotary_table(), scale=self.scale, window=self.window, ctx=ctx,
-            view=cache, write=write, **self.sinks, **self.extra)
+            view=pages, write=write, **self.sinks, **self.extra)
+        if self.gate_kind is not None:
+            # (the heads' outputs may have rows of the pages' size: the gate leaves the values)
+            mixed = self.ops.gate_heads(mixed, gate, heads=self.heads, row_dim=self.row_dim,
+                                        value_dim=self.value_dim,
+                                        per_head=self.gate_kind == "heads")
         if residual is None:
             return self.ops.linear(mixed, self.out)
         if self.residual_scale != 1.0:
@@ -601,3 +689,89 @@ class DifferentialAttention(Mixer):
                                               value_dim=self.value_dim, mix=self.mix, eps=self.eps,
                                               factor=1.0 - self.diff)
         return self.ops.linear(mixed, self.out)
+
+
+@MIXERS.register("mamba2")
+class SelectiveStateSpace(Mixer):
+    """A selective state space in the form of Mamba-2: one matrix state S [state, value_dim] per
+    head, kept in 32-bit from token to token. Parameters: ``hidden``, ``heads``, ``value_dim``,
+    ``state`` (N), ``groups`` (G; head h reads group h // (heads / groups)), ``taps``,
+    ``norm_groups``, ``eps``.
+
+    With inner = heads * value_dim, W_in x is laid out as [z: inner | x: inner | B: G N | C: G N |
+    dt: heads]. x, B and C together pass a causal convolution over the last ``taps`` tokens of
+    their request on every channel (``conv`` [channels, taps], last column the current token's,
+    ``conv_bias``) and silu. dt = softplus(dt + dt_bias). Per token and head: S = exp(-exp(A_log)
+    dt) S + dt B x^T; y = S^T C + D x. The heads' outputs side by side are multiplied by silu(z),
+    divided by their root mean square in ``norm_groups`` equal parts (each part by its own, with
+    ``eps``), multiplied by ``norm`` and projected by W_o. Everything after the convolution's
+    silu is 32-bit. A request keeps S of every head in a 32-bit slot and the convolution's last
+    taps - 1 inputs in a slot of the compute dtype."""
+
+    @classmethod
+    def _sizes(cls, spec):
+        inner = spec["heads"] * spec["value_dim"]
+        return inner, inner + 2 * spec["groups"] * spec["state"]
+
+    @classmethod
+    def tensors(cls, spec):
+        hidden, heads = spec["hidden"], spec["heads"]
+        inner, channels = cls._sizes(spec)
+        return {"in": TensorSpec((inner + channels + heads, hidden)),
+                "conv": TensorSpec((channels, spec["taps"]), "wide"),
+                "conv_bias": TensorSpec((channels,), "bias"),
+                "dt_bias": TensorSpec((heads,), "wide"), "A_log": TensorSpec((heads,), "wide"),
+                "D": TensorSpec((heads,), "norm"), "norm": TensorSpec((inner,), "norm"),
+                "o": TensorSpec((hidden, inner))}
+
+    @classmethod
+    def cache_need(cls, spec):
+        _, channels = cls._sizes(spec)
+        need = {"state": FixedState((spec["heads"] * spec["state"] * spec["value_dim"],), "float32")}
+        if spec["taps"] > 1:
+            need["inputs"] = FixedState((spec["taps"] - 1, channels))
+        return need
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.sizes = dict(heads=spec["heads"], value_dim=spec["value_dim"], state_dim=spec["state"],
+                          groups=spec["groups"])
+        if spec["heads"] % spec["groups"]:
+            raise ValueError("heads must be a multiple of groups")
+        self.inner, self.channels = self._sizes(spec)
+        self.taps, self.norm_groups = int(spec["taps"]), int(spec["norm_groups"])
+        if self.inner % self.norm_groups:
+            raise ValueError("the heads' outputs must split into equal parts for the norm")
+        self.project = self.matrix(tensors["in"])
+        self.conv = self.vector(tensors["conv"])
+        self.conv_bias = self.vector(tensors["conv_bias"])
+        self.dt_bias = self.vector(tensors["dt_bias"])
+        self.a_log = self.vector(tensors["A_log"])
+        self.skip = self.vector(tensors["D"])
+        self.norm = self.vector(tensors["norm"])
+        self.out = self.matrix(tensors["o"])
+        self.eps = float(spec["eps"])
+
+    accepts_normed_input = True
+
+    def input_projection(self):
+        return self.project, None
+
+    def forward(self, x, ctx, cache, write):
+        return self.forward_projected(self.ops.linear(x, self.project), ctx, cache, write)
+
+    def forward_projected(self, projected, ctx, cache, write, residual=None):
+        inner, channels = self.inner, self.channels
+        mixed = self.ops.channel_conv(projected[:, inner:inner + channels], self.conv,
+                                      self.conv_bias, taps=self.taps, activation="silu", ctx=ctx,
+                                      view=cache.get("inputs"), write=write)
+        y = self.ops.state_space_scan(mixed, projected[:, inner + channels:], a_log=self.a_log,
+                                      dt_bias=self.dt_bias, skip=self.skip, ctx=ctx,
+                                      view=cache["state"], write=write, **self.sizes)
+        gated = self.ops.gated_group_norm(y, projected[:, :inner], self.norm,
+                                          groups=self.norm_groups, eps=self.eps,
+                                          dtype=self.runtime.dtype)
+        out = self.ops.linear(gated, self.out)
+        if residual is not None:
+            raise ValueError("this mixer hands its output back")
+        return out

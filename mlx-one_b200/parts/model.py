@@ -169,6 +169,7 @@ class Model:
                 if call.inject.mix not in self.mixing:
                     self.mixing[call.inject.mix] = matrix.to(runtime.dtype).contiguous()
         self.softcap = None if spec.logit_softcap is None else float(spec.logit_softcap)
+        self.logit_scale = float(spec.logit_scale)
         # the factor with which the pending output of the last forward is still to be added
         self.pending_scale = 1.0
         self.cache_needs = cache_entries(spec)
@@ -263,6 +264,8 @@ class Model:
         else:
             normed = self.final_norm.forward(picked, picked_delta, **extra)
         logits = self.ops.linear(normed, self.head, out_dtype=torch.float32)
+        if self.logit_scale != 1.0:
+            self.ops.scale_values(logits, self.logit_scale)
         if self.softcap is not None:
             self.ops.softcap(logits, self.softcap)
         return logits

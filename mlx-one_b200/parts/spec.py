@@ -104,6 +104,8 @@ class ModelSpec:
     vectors: Mapping[str, Any] = field(default_factory=dict)
     # logits become cap * tanh(logits / cap); None: the output product's values as they are
     logit_softcap: float | None = None
+    # a factor on the output product's values (applied before a cap)
+    logit_scale: float = 1.0
     # an embedding part (registry EMBEDDINGS) that makes the stream's first value; None: row
     # ``token`` of the table ``embedding``. Its table is stored under ``embedding`` all the same.
     embedding_part: PartSpec | None = None

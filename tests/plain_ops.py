@@ -151,13 +151,14 @@ class PlainOps:
         return q.contiguous()
 
     def qkv_attention(self, qkv, *, heads, kv_heads, head_dim, q_weight, k_weight, eps, rotary,
-                      scale, window, ctx, view, write, sinks=None, chunk=None, **extra):
+                      scale, window, ctx, view, write, sinks=None, chunk=None, keep_first=0,
+                      **extra):
         q = self.qk_norm_rope_store(qkv, heads=heads, kv_heads=kv_heads, head_dim=head_dim,
                                     q_weight=q_weight, k_weight=k_weight, eps=eps, rotary=rotary,
                                     ctx=ctx, view=view, write=write, **extra)
         return self.paged_attention(q, heads=heads, kv_heads=kv_heads, head_dim=view.kv.shape[-1],
                                     scale=scale, window=window, ctx=ctx, view=view, sinks=sinks,
-                                    chunk=chunk)
+                                    chunk=chunk, keep_first=keep_first)
 
     def concat_stream(self, residual, delta, token_ids, table, dtype, delta_scale=1.0):
         stream = residual if delta is None else residual + delta.float() * delta_scale
@@ -412,7 +413,7 @@ class PlainOps:
         return out.reshape(tokens, inner).to(projected.dtype)
 
     def paged_attention(self, q, *, heads, kv_heads, head_dim, scale, window, ctx, view,
-                        sinks=None, chunk=None):
+                        sinks=None, chunk=None, keep_first=0):
         tokens = q.shape[0]
         out = torch.empty(tokens, heads, head_dim)
         positions = ctx.positions.tolist()
@@ -424,7 +425,7 @@ class PlainOps:
             lowest = max(p - window + 1, 0) if window else 0
             if chunk:
                 lowest = max(lowest, p - p % chunk)
-            keys = list(range(lowest, p + 1))
+            keys = list(range(min(keep_first, lowest))) + list(range(lowest, p + 1))
             pages = [table[requests[t]][key // view.page_size] for key in keys]
             assert min(pages) >= 0, "a key is read from a position without a page"
             offsets = [key % view.page_size for key in keys]
@@ -439,6 +440,101 @@ class PlainOps:
                 v = torch.cat([v, torch.zeros_like(v[:1])], dim=0)
             out[t] = torch.einsum("hk,khd->hd", torch.softmax(scores, dim=-1), v)
         return out.reshape(tokens, heads * head_dim).to(q.dtype)
+
+    def channel_conv(self, rows, kernel, bias, *, taps, activation, ctx, view, write):
+        tokens, channels = rows.shape
+        dtype = rows.dtype
+        flat = rows.float()
+        out = torch.empty(tokens, channels)
+        starts = ctx.request_start.tolist()
+        history = ctx.history.tolist()
+        for r in range(ctx.requests):
+            first, last = starts[r], starts[r + 1]
+            n = last - first
+            if taps > 1:
+                state = view.state[int(view.slots[r])]                  # [taps - 1, channels]
+                valid = torch.arange(taps - 1) + history[r] - (taps - 1) >= 0
+                padded = torch.cat((state.float() * valid[:, None], flat[first:last]), dim=0)
+            else:
+                padded = flat[first:last]
+            y = torch.zeros(n, channels)
+            for j in range(taps):
+                y = y + padded[j:j + n] * kernel[:, j]
+            if bias is not None:
+                y = y + bias
+            out[first:last] = y
+            if write and taps > 1:
+                state[:] = padded[n:n + taps - 1].to(state.dtype)
+        if activation == "silu":
+            out = out / (1 + torch.exp(-out))
+        elif activation is not None:
+            raise ValueError(activation)
+        return out.to(dtype)
+
+    def gate_heads(self, mixed, gate, *, heads, row_dim, value_dim, per_head):
+        tokens = mixed.shape[0]
+        values = mixed.float().view(tokens, heads, row_dim)[:, :, :value_dim]
+        g = torch.sigmoid(gate.float())
+        g = g.view(tokens, heads, 1) if per_head else g.view(tokens, heads, value_dim)
+        return (values * g).reshape(tokens, heads * value_dim).to(mixed.dtype)
+
+    def state_space_scan(self, mixed, steps, *, a_log, dt_bias, skip, ctx, view, write, heads,
+                         value_dim, state_dim, groups):
+        tokens = mixed.shape[0]
+        inner, wide = heads * value_dim, groups * state_dim
+        flat = mixed.float()
+        x = flat[:, :inner].view(tokens, heads, value_dim)
+        b = flat[:, inner:inner + wide].view(tokens, groups, state_dim)
+        c = flat[:, inner + wide:].view(tokens, groups, state_dim)
+        dt = torch.nn.functional.softplus(steps.float() + dt_bias, threshold=30.0)
+        decay = torch.exp(-torch.exp(a_log) * dt)
+        out = torch.empty(tokens, heads, value_dim)
+        starts, slots = ctx.request_start.tolist(), view.slots.tolist()
+        per = heads // groups
+        for r in range(ctx.requests):
+            state = view.state[slots[r]].view(heads, state_dim, value_dim).clone()
+            for t in range(starts[r], starts[r + 1]):
+                bt = b[t].repeat_interleave(per, dim=0)              # [heads, state]
+                ct = c[t].repeat_interleave(per, dim=0)
+                state = decay[t][:, None, None] * state + \
+                    (dt[t][:, None] * bt)[:, :, None] * x[t][:, None, :]
+                out[t] = torch.einsum("hnp,hn->hp", state, ct) + skip[:, None] * x[t]
+            if write:
+                view.state[slots[r]] = state.reshape(-1)
+        return out.reshape(tokens, inner)
+
+    def gated_group_norm(self, y, gate, weight, *, groups, eps, dtype):
+        tokens, inner = y.shape
+        z = gate.float()
+        v = (y * (z / (1 + torch.exp(-z)))).view(tokens, groups, inner // groups)
+        v = v * torch.rsqrt(v.pow(2).mean(dim=-1, keepdim=True) + eps)
+        return (v.reshape(tokens, inner) * weight).to(dtype)
+
+    def route_general(self, x, router, correction, *, experts, identity, top, scores, normalize,
+                      shared_gate):
+        logits = x.float() @ router.T
+        outputs = experts + identity
+        z = logits[:, :outputs]
+        s = torch.softmax(z, dim=-1) if scores == "softmax" else torch.sigmoid(z)
+        choice = s if correction is None else s + correction
+        tokens = s.shape[0]
+        weights = torch.zeros(tokens, outputs)
+        for t in range(tokens):
+            chosen = sorted(range(outputs), key=lambda e: (-float(choice[t, e]), e))[:top]
+            total = sum(float(s[t, e]) for e in chosen) + 1e-20 if normalize else 1.0
+            for e in chosen:
+                weights[t, e] = float(s[t, e]) / total
+        others = torch.zeros(2, tokens)
+        others[0] = weights[:, experts:].sum(dim=-1)
+        if shared_gate:
+            others[1] = torch.sigmoid(logits[:, outputs])
+        return weights[:, :experts].contiguous(), others
+
+    def add_scaled_rows(self, out, x, factors):
+        out.copy_((out.float() + x.float() * factors[:, None]).to(out.dtype))
+
+    def scale_values(self, values, factor):
+        values.mul_(factor)
 
     def argmax(self, logits):
         return torch.argmax(logits, dim=-1).to(torch.int32)
