@@ -96,10 +96,11 @@ struct Pages {
 };
 
 // Copies keys first..first+KEYS-1 of one key head into a K and a V tile; rows outside [lowest,
-// last] or without a page are zero. `lanes` threads take part, this one is `lane`.
+// last] (but for those below `kept`, the first positions that stay visible behind a window) or
+// without a page are zero. `lanes` threads take part, this one is `lane`.
 template <int HD, int KEYS>
 __device__ __forceinline__ void load_tile(bf16* k_tile, bf16* v_tile, const Pages& pages, int first,
-                                          int lowest, int last, int lane, int lanes) {
+                                          int lowest, int last, int lane, int lanes, int kept = 0) {
     using T = Tile<HD>;
     if (lanes == 32 && pages.page_shift >= 0) {
         // One warp, pages of a power of two: lane j looks up the tile's j-th page once and the
@@ -114,7 +115,7 @@ __device__ __forceinline__ void load_tile(bf16* k_tile, bf16* v_tile, const Page
             const int row = piece / T::CHUNKS, chunk = piece % T::CHUNKS;
             const int key = first + row;
             const int page = __shfl_sync(0xffffffffu, my_page, (inside + row) >> pages.page_shift);
-            const bool live = key >= lowest && key <= last && page >= 0;
+            const bool live = (key >= lowest || key < kept) && key <= last && page >= 0;
             const size_t offset =
                 live ? (((size_t)page * pages.kv_heads + pages.kv_head) * pages.page_size +
                         ((inside + row) & (pages.page_size - 1))) * HD + chunk * 8
@@ -128,7 +129,7 @@ __device__ __forceinline__ void load_tile(bf16* k_tile, bf16* v_tile, const Page
     for (int piece = lane; piece < KEYS * T::CHUNKS; piece += lanes) {
         const int row = piece / T::CHUNKS, chunk = piece % T::CHUNKS;
         const int key = first + row;
-        bool live = key >= lowest && key <= last;
+        bool live = (key >= lowest || key < kept) && key <= last;
         size_t offset = 0;
         if (live) {
             const int block = pages.page_shift >= 0 ? key >> pages.page_shift : key / pages.page_size;
@@ -154,7 +155,7 @@ __device__ __forceinline__ void attend_tile(const uint32_t (&qf)[HD / 16][4], co
                                             const bf16* v_tile, int first, const int (&limit_lo)[2],
                                             const int (&limit_hi)[2], float scale_log2,
                                             float (&m)[2], float (&l)[2], float (&o)[HD / 8][4],
-                                            int lane) {
+                                            int lane, int kept = 0) {
     using T = Tile<HD>;
     float s[KEYS / 8][4];
 #pragma unroll
@@ -185,7 +186,7 @@ __device__ __forceinline__ void attend_tile(const uint32_t (&qf)[HD / 16][4], co
             const int i = c >> 1;
             if (MASKED) {
                 const int key = first + j * 8 + t2 + (c & 1);
-                if (!(key >= limit_lo[i] && key <= limit_hi[i])) s[j][c] = -INFINITY;
+                if (!((key >= limit_lo[i] || key < kept) && key <= limit_hi[i])) s[j][c] = -INFINITY;
             }
             tile_max[i] = fmaxf(tile_max[i], s[j][c]);
         }
@@ -251,7 +252,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
                          const int* __restrict__ block_table, int table_width, int page_size,
                          const int* __restrict__ request_start, const int* __restrict__ history,
                          bf16* __restrict__ out, int requests, int heads, int kv_heads,
-                         float scale_log2, int window, const float* __restrict__ sinks) {
+                         float scale_log2, int window, const float* __restrict__ sinks,
+                         int keep_first) {
     using T = Tile<HD>;
     constexpr int KEYS = PREFILL_KEYS;
     extern __shared__ __align__(16) unsigned char shared_bytes[];
@@ -299,9 +301,16 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
     const int last_position = first_position + rows - 1;
     const int lowest = first_visible_key(first_position, window);
     const int tile_first = lowest / KEYS, tile_last = last_position / KEYS;
+    // The first positions that stay visible behind a window: their tiles come first, the tiles
+    // between them and the window's first are skipped. Tiles are counted in the order they are
+    // walked (`turn`); turn_tile gives the tile's place among the keys.
+    const int kept = min(keep_first, lowest);
+    const int kept_tiles = min((kept + KEYS - 1) / KEYS, tile_first);
+    const int turns = kept_tiles + tile_last - tile_first + 1;
+    auto turn_tile = [&](int turn) { return turn < kept_tiles ? turn : tile_first + turn - kept_tiles; };
 
-    load_tile<HD, KEYS>(k_tiles, v_tiles, pages, tile_first * KEYS, lowest, last_position, threadIdx.x,
-                  PREFILL_WARPS * 32);
+    load_tile<HD, KEYS>(k_tiles, v_tiles, pages, turn_tile(0) * KEYS, lowest, last_position,
+                        threadIdx.x, PREFILL_WARPS * 32, keep_first);
     copy_commit();
 
     // per-thread rows: lane/4 and lane/4 + 8 of the warp's 16
@@ -333,12 +342,14 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
     const bool warp_whole = warp * 16 + 15 < rows;
     const int open_lo = first_visible_key(warp_first + 15, window);
 
-    for (int tile = tile_first; tile <= tile_last; ++tile) {
-        const int buffer = (tile - tile_first) & 1;
-        if (tile < tile_last) {
+    for (int turn = 0; turn < turns; ++turn) {
+        const int tile = turn_tile(turn);
+        const int buffer = turn & 1;
+        if (turn + 1 < turns) {
             load_tile<HD, KEYS>(k_tiles + (buffer ^ 1) * KEYS * T::STRIDE,
-                          v_tiles + (buffer ^ 1) * KEYS * T::STRIDE, pages, (tile + 1) * KEYS,
-                          lowest, last_position, threadIdx.x, PREFILL_WARPS * 32);
+                          v_tiles + (buffer ^ 1) * KEYS * T::STRIDE, pages,
+                          turn_tile(turn + 1) * KEYS, lowest, last_position, threadIdx.x,
+                          PREFILL_WARPS * 32, keep_first);
             copy_commit();
             copy_wait<1>();
         } else {
@@ -365,7 +376,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
                                              scale_log2, m, l, o, lane);
             else
                 attend_tile<HD, KEYS, true>(qf, k_now, v_now, tile * KEYS, limit_lo, limit_hi,
-                                            scale_log2, m, l, o, lane);
+                                            scale_log2, m, l, o, lane, keep_first);
         }
         __syncthreads();
     }
@@ -424,6 +435,7 @@ struct DecodePrep {
     bf16* cache = nullptr;                // the writable cache (keys, then values after kv_half)
     int write_kv = 0;
     int* error_flag = nullptr;
+    int keep_first = 0;                   // positions below this stay visible behind a window
 };
 
 template <int HD, bool CLUSTER, bool PREP>
@@ -451,10 +463,16 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
 
     const int position = positions[request];
     const int lowest = first_visible_key(position, window);
-    const int tile_first = lowest / KEYS, tile_count = position / KEYS - tile_first + 1;
+    // Tiles are counted in the order they are walked: first those of the first positions that
+    // stay visible behind a window, then the window's; tile_at gives a tile's place among the keys.
+    const int kept = min(prep.keep_first, lowest);
+    const int tile_first = lowest / KEYS;
+    const int kept_tiles = min((kept + KEYS - 1) / KEYS, tile_first);
+    const int tile_count = kept_tiles + position / KEYS - tile_first + 1;
+    auto tile_at = [&](int turn) { return turn < kept_tiles ? turn : tile_first + turn - kept_tiles; };
     const int per_split = (tile_count + splits - 1) / splits;
-    const int my_first = tile_first + split * per_split;
-    const int my_last = min(my_first + per_split, tile_first + tile_count) - 1;
+    const int my_first = split * per_split;
+    const int my_last = min(my_first + per_split, tile_count) - 1;
 
     Pages pages{kv, kv + kv_half, block_table + (size_t)request * table_width, table_width,
                 page_size, kv_heads, kv_head,
@@ -466,12 +484,12 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
     // before the one that holds them are what earlier steps left, and are asked for before that
     // kernel is waited for, so that they are on their way while it finishes.
     int tile = my_first + warp;
-    const int newest = position / KEYS;
+    const int newest = tile_count - 1;
     auto fetch = [&](int ahead) {
         const int coming = tile + ahead * DECODE_WARPS;
         if (coming <= my_last)
             load_tile<HD, KEYS>(ring + ahead * STAGE, ring + ahead * STAGE + KEYS * T::STRIDE, pages,
-                                coming * KEYS, lowest, position, lane, 32);
+                                tile_at(coming) * KEYS, lowest, position, lane, 32, kept);
         copy_commit();
     };
     int ahead = 0;
@@ -640,12 +658,12 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
             const int into = (stage + DECODE_STAGES - 1) % DECODE_STAGES;
             if (coming <= my_last)
                 load_tile<HD, KEYS>(ring + into * STAGE, ring + into * STAGE + KEYS * T::STRIDE,
-                                    pages, coming * KEYS, lowest, position, lane, 32);
+                                    pages, tile_at(coming) * KEYS, lowest, position, lane, 32, kept);
             copy_commit();
         }
         const bf16* k_tile = ring + stage * STAGE;
         const bf16* v_tile = k_tile + KEYS * T::STRIDE;
-        const int first = tile * KEYS;
+        const int first = tile_at(tile) * KEYS;
         if (PREP && tile == newest && prep.write_kv) {
             // The token's own key and value, prepared before the loop: put into the tile over
             // what the copy brought, and written to the request's page by the first block of
@@ -694,7 +712,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int key = first + mt * 16 + g + (c >> 1) * 8;
-                const bool seen = key >= lowest && key <= position && head_live[c & 1];
+                const bool seen = (key >= lowest || key < kept) && key <= position && head_live[c & 1];
                 s[mt][c] = seen ? s[mt][c] * scale_log2 : -INFINITY;
                 tile_max[c & 1] = fmaxf(tile_max[c & 1], s[mt][c]);
             }
@@ -910,7 +928,7 @@ template <int HD>
 int launch_prefill(const void* q, const void* kv, long long kv_half, const int* block_table,
                    int table_width, int page_size, const int* request_start, const int* history,
                    void* out, int tokens, int requests, int heads, int kv_heads, float scale,
-                   int window, const float* sinks, cudaStream_t stream) {
+                   int window, const float* sinks, cudaStream_t stream, int keep_first = 0) {
     using T = Tile<HD>;
     const size_t shared = (size_t)(ROWS + 4 * PREFILL_KEYS) * T::STRIDE * 2;
     auto kernel = attention_prefill_kernel<HD>;
@@ -920,7 +938,7 @@ int launch_prefill(const void* q, const void* kv, long long kv_half, const int* 
     kernel<<<grid, PREFILL_WARPS * 32, shared, stream>>>(
         (const bf16*)q, (const bf16*)kv, kv_half, block_table, table_width, page_size,
         request_start, history, (bf16*)out, requests, heads, kv_heads, scale * LOG2E, window,
-        sinks);
+        sinks, keep_first);
     return 0;
 }
 
@@ -1039,6 +1057,33 @@ MLXONE_API int mlxone_attention_prefill(const void* q, const void* kv, const int
     return 0;
 }
 
+// ... with a window behind which the first `keep_first` positions of a sequence stay visible
+MLXONE_API int mlxone_attention_prefill_keep(const void* q, const void* kv, const int* block_table,
+                                             int table_width, int page_size, int pages,
+                                             const int* request_start, const int* history,
+                                             void* out, int tokens, int requests, int heads,
+                                             int kv_heads, int head_dim, float scale, int window,
+                                             int keep_first, const float* sinks,
+                                             cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    MLXONE_REQUIRE(tokens > 0 && requests > 0 && heads > 0 && kv_heads > 0 &&
+                       heads % kv_heads == 0, "attention_prefill: bad sizes");
+    MLXONE_REQUIRE(heads <= 65535, "attention_prefill: too many heads");
+    MLXONE_REQUIRE(page_size > 0 && pages > 0 && table_width > 0,
+                   "attention_prefill: bad page geometry");
+    MLXONE_REQUIRE(keep_first >= 0 && (keep_first == 0 || window > 0),
+                   "attention_prefill: first positions are kept behind a window only");
+    const long long kv_half = (long long)pages * kv_heads * page_size * head_dim;
+#define CALL(HD)                                                                              \
+    launch_prefill<HD>(q, kv, kv_half, block_table, table_width, page_size, request_start,    \
+                       history, out, tokens, requests, heads, kv_heads, scale, window, sinks,  \
+                       stream, keep_first)
+    MLXONE_HEAD_DIMS(CALL)
+#undef CALL
+    MLXONE_LAUNCH_CHECK("attention_prefill");
+    return 0;
+}
+
 // Floats of scratch that the decode kernel needs for `splits` > 1.
 MLXONE_API long long mlxone_attention_decode_scratch(int requests, int heads, int head_dim,
                                                      int splits) {
@@ -1066,6 +1111,37 @@ MLXONE_API int mlxone_attention_decode_sinks(const void* q, const void* kv, cons
 #define CALL(HD)                                                                               \
     launch_decode<HD, false>(q, kv, kv_half, block_table, table_width, page_size, positions, out, \
                              partial, requests, heads, kv_heads, splits, scale, window, sinks, stream)
+    MLXONE_HEAD_DIMS(CALL)
+#undef CALL
+    MLXONE_LAUNCH_CHECK("attention_decode");
+    return 0;
+}
+
+// ... with a window behind which the first `keep_first` positions of a sequence stay visible
+MLXONE_API int mlxone_attention_decode_keep(const void* q, const void* kv, const int* block_table,
+                                            int table_width, int page_size, int pages,
+                                            const int* positions, void* out, float* partial,
+                                            int requests, int heads, int kv_heads, int head_dim,
+                                            int splits, float scale, int window, int keep_first,
+                                            const float* sinks, cudaStream_t stream) {
+    if (requests == 0) return 0;
+    MLXONE_REQUIRE(requests > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
+                   "attention_decode: bad sizes");
+    MLXONE_REQUIRE(requests <= 65535 && splits >= 1 && splits <= 65535,
+                   "attention_decode: at most 65535 requests and splits");
+    MLXONE_REQUIRE(splits <= 8 || partial != nullptr,
+                   "attention_decode: more than 8 splits need a scratch buffer");
+    MLXONE_REQUIRE(page_size > 0 && pages > 0 && table_width > 0,
+                   "attention_decode: bad page geometry");
+    MLXONE_REQUIRE(keep_first >= 0 && (keep_first == 0 || window > 0),
+                   "attention_decode: first positions are kept behind a window only");
+    const long long kv_half = (long long)pages * kv_heads * page_size * head_dim;
+    DecodePrep prep;
+    prep.keep_first = keep_first;
+#define CALL(HD)                                                                               \
+    launch_decode<HD, false>(q, kv, kv_half, block_table, table_width, page_size, positions, out, \
+                             partial, requests, heads, kv_heads, splits, scale, window, sinks,  \
+                             stream, prep)
     MLXONE_HEAD_DIMS(CALL)
 #undef CALL
     MLXONE_LAUNCH_CHECK("attention_decode");

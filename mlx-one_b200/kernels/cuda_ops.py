@@ -1268,7 +1268,9 @@ class CudaOps:
             if sinks.numel() != heads:
                 raise KernelError("one sink per query head")
         keep_first = int(keep_first or 0) if window > 0 else 0
-        if keep_first:
+        tensor_cores = (self.tensor_core_attention
+                        and self.lib.mlxone_attention_mma_supports(head_dim, code))
+        if keep_first and not tensor_cores:
             self._call("mlxone_attention_generic_keep", _c_void_p(_ptr(q)), _c_void_p(_ptr(view.kv)),
                        _c_void_p(_ptr(view.block_table)), _c_int(width), _c_int(view.page_size),
                        _c_int(pages), _c_void_p(_ptr(ctx.positions)),
@@ -1277,10 +1279,10 @@ class CudaOps:
                        _c_int(window), _c_int(keep_first), _c_int(code), _c_void_p(_ptr(sinks)),
                        _c_void_p(_ptr(self.error_flag)))
             return out
-        if self.tensor_core_attention and self.lib.mlxone_attention_mma_supports(head_dim, code):
+        if tensor_cores:
             if ctx.max_portion == 1 and tokens == ctx.requests:
                 self._decode_attention(q, out, ctx.requests, heads, kv_heads, head_dim, scale,
-                                       window, ctx, view, sinks)
+                                       window, ctx, view, sinks, keep_first)
                 return out
             # The decodes at the head of a mixed step go to the split-key kernel, which reads
             # each request's keys once for all its query heads; as one-token portions in the
@@ -1290,13 +1292,23 @@ class CudaOps:
                 singles = 0
             if singles:
                 self._decode_attention(q, out, singles, heads, kv_heads, head_dim, scale, window,
-                                       ctx, view, sinks)
+                                       ctx, view, sinks, keep_first)
             # the other requests: the tables, starts and histories from request ``singles`` on
             # (token numbers in request_start stay those of the whole step)
             rest = ctx.requests - singles
             table = view.block_table[singles:]
             starts, history = ctx.request_start[singles:], ctx.history[singles:]
-            if (self.tcgen05_attention and q.dtype == torch.bfloat16
+            if keep_first:
+                # (the tcgen05 kernel walks one run of key tiles; the kept first positions are a
+                # second run, which the mma.sync kernel takes)
+                self._call("mlxone_attention_prefill_keep", _c_void_p(_ptr(q)),
+                           _c_void_p(_ptr(view.kv)), _c_void_p(_ptr(table)),
+                           _c_int(width), _c_int(view.page_size), _c_int(pages),
+                           _c_void_p(_ptr(starts)), _c_void_p(_ptr(history)),
+                           _c_void_p(_ptr(out)), _c_int(tokens), _c_int(rest),
+                           _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_float(scale),
+                           _c_int(window), _c_int(keep_first), _c_void_p(_ptr(sinks)))
+            elif (self.tcgen05_attention and q.dtype == torch.bfloat16
                     and self.lib.mlxone_attention_tcgen05_supports(
                         _c_int(head_dim), _c_int(heads), _c_int(kv_heads), _c_int(view.page_size))):
                 # few query tiles (a prompt's portion beside a step's decodes): their keys are
@@ -1346,12 +1358,22 @@ class CudaOps:
         return out
 
     def _decode_attention(self, q, out, requests, heads, kv_heads, head_dim, scale, window, ctx,
-                          view, sinks=None) -> None:
+                          view, sinks=None, keep_first=0) -> None:
         """The split-key kernel for the first ``requests`` requests of the step, one token each
         (token i is request i's): rows 0 to requests - 1 of q, positions, table and out."""
         width = view.block_table.shape[1]
         splits, partial = self._decode_plan(requests, heads, kv_heads, head_dim, width, window,
-                                            view)
+                                            view, keep_first)
+        if keep_first:
+            self._call("mlxone_attention_decode_keep", _c_void_p(_ptr(q)), _c_void_p(_ptr(view.kv)),
+                       _c_void_p(_ptr(view.block_table)), _c_int(width), _c_int(view.page_size),
+                       _c_int(view.kv.shape[1]), _c_void_p(_ptr(ctx.positions)),
+                       _c_void_p(_ptr(out)), _c_void_p(_ptr(partial)), _c_int(requests),
+                       _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(splits),
+                       _c_float(scale), _c_int(window), _c_int(keep_first), _c_void_p(_ptr(sinks)))
+            if partial is not None:
+                self.launches += 1          # the merge kernel
+            return
         self._call("mlxone_attention_decode_sinks", _c_void_p(_ptr(q)), _c_void_p(_ptr(view.kv)),
                    _c_void_p(_ptr(view.block_table)), _c_int(width), _c_int(view.page_size),
                    _c_int(view.kv.shape[1]), _c_void_p(_ptr(ctx.positions)), _c_void_p(_ptr(out)),
@@ -1361,11 +1383,11 @@ class CudaOps:
         if partial is not None:
             self.launches += 1          # the merge kernel
 
-    def _decode_plan(self, requests, heads, kv_heads, head_dim, width, window, view):
+    def _decode_plan(self, requests, heads, kv_heads, head_dim, width, window, view, keep_first=0):
         """Key splits of a decode attention launch and the scratch for their partial results
         (None when a thread-block cluster merges them, or there is one split)."""
         splits = self.decode_splits(requests, heads, kv_heads, head_dim, width * view.page_size,
-                                    window)
+                                    window, keep_first)
         clustered = self.cluster_merge and splits <= min(self.cluster_merge_max_splits, 8)
         partial = None
         if splits > 1 and not clustered:
@@ -1374,11 +1396,11 @@ class CudaOps:
         return splits, partial
 
     def decode_splits(self, requests: int, heads: int, kv_heads: int, head_dim: int,
-                      context_bound: int, window: int | None) -> int:
+                      context_bound: int, window: int | None, keep_first: int = 0) -> int:
         """Into how many parts the decode kernel cuts a request's keys: as many blocks as the
         GPU holds at once (one wave), but at least four tiles of 32 keys per part."""
         if window:
-            context_bound = min(context_bound, abs(window) + 31)
+            context_bound = min(context_bound, abs(window) + 31 + (-(-keep_first // 32)) * 32)
         tiles = max(-(-context_bound // 32), 1)
         blocks_per_sm = self.lib.mlxone_attention_decode_resident(_c_int(head_dim))
         groups = kv_heads * (-(-(heads // kv_heads) // 8))
