@@ -19,6 +19,8 @@ Two more workloads, each printing one JSON line of its own (the default line is 
     python bench.py --case long         4 x 32,768-token prompts at the LFM2-350M shape, then decoding
     python bench.py --case lamisun      Lamisun beside LFM2 at equal width, depth and vocabulary:
                                         decode and prefill tokens/s, and the new kernels alone
+    python bench.py --case tirudra      Tirudra beside Farorax at equal width, depth and vocabulary:
+                                        decode and prefill tokens/s, and the new kernels alone
     python bench.py --case farorax      Farorax beside Galarax at equal width, depth and vocabulary:
                                         decode and prefill tokens/s, and the new kernels alone
     python bench.py --case galarax      Galarax beside LFM2 at equal width, depth and vocabulary:
@@ -230,7 +232,8 @@ def model_flops(spec, tokens):
             if part.kind == "attention":
                 width = part["heads"] * part["head_dim"]
                 window = part.get("window") or tokens
-                seen = sum(min(i + 1, window) for i in range(tokens))
+                kept = part.get("keep_first") or 0
+                seen = sum(min(i + 1, window + min(kept, max(i + 1 - window, 0))) for i in range(tokens))
                 flops += 4 * width * seen                       # causal (windowed) QK^T and PV
             elif part.kind == "latent_attention":
                 # every head's query against the one row per token, and the weights' average of
@@ -244,6 +247,8 @@ def model_flops(spec, tokens):
             elif part.kind == "lightning":
                 # 32-bit multiply-adds of the recurrence (not tensor-core work, but work)
                 flops += 4 * tokens * part["heads"] * part["key_dim"] * part["value_dim"]
+            elif part.kind == "mamba2":
+                flops += 4 * tokens * part["heads"] * part["state"] * part["value_dim"]
     return flops
 
 
@@ -1126,6 +1131,261 @@ def case_farorax(args) -> int:
     return 0
 
 
+# --------------------------------------------------------------------------- Tirudra beside Farorax
+
+
+def tirudra_shape(width: int, layers: int, vocab: int = 65536) -> dict:
+    """A Tirudra of the sizes that a model of this width has: state spaces in every other layer
+    (heads of 64 values with states of 128, inner width = model width, four taps), between them in
+    turn attention over a window of 1024 that keeps four tokens (heads of 64, one key head per
+    four query heads, three taps, the whole head rotated) and attention whose values are its keys;
+    eight routed experts of the model's width and two identity outputs of which a token uses
+    three, beside a gated shared expert."""
+    rot = {"base": 1000000.0, "dims": 64}
+    attention = {"heads": width // 64, "kv_heads": width // 256, "dim": 64, "vdim": 64,
+                 "scale": 0.125, "conv": 3, "mask": {"size": 1024, "keep_first": 4},
+                 "rot": dict(rot, scaling={"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0})}
+    shared = {"heads": width // 64, "kv_heads": width // 256, "dim": 64, "vdim": 64, "scale": 0.125,
+              "rot": dict(rot, scaling={"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192})}
+    space = {"heads": width // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4,
+             "norm_groups": width // 256}
+    routed = {"kind": "moe", "expert": {"ff": width}, "shared": {"ff": width},
+              "router": {"experts": 8, "top": 3, "identity": 2}}
+    entries = []
+    for index in range(layers):
+        mixer = (("mamba2", space), ("attention", attention), ("mamba2", space),
+                 ("attention_2", shared))[index % 4]
+        entries.append({"type": mixer[0], "mixer": mixer[1], "mlp": routed})
+    return {"architecture": "Tirudra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "logit_scale": 0.25, "layers": entries}
+
+
+def tirudra_kernels(width, batch, peak):
+    """The kernels that Tirudra adds, alone, beside the like kernels of Farorax, for a decode step
+    of ``batch`` tokens and a prompt of PREFILL_TOKENS tokens: algorithmic bytes (or flops) /
+    time against the measured peaks. Arguments rotate over copies that together exceed L2."""
+    import torch
+
+    from mlx_one_b200.kernels import default_ops
+    from mlx_one_b200.parts import (FixedState, PagedKeyValues, PagedView, StateView,
+                                    StepContext)
+
+    ops, device = default_ops("cuda:0"), "cuda:0"
+    ints = lambda values: torch.tensor(values, dtype=torch.int32, device=device)
+    bf16 = lambda *shape: torch.randn(*shape, device=device).bfloat16()
+
+    def ctx_of(portions, histories):
+        positions, owner, starts = [], [], [0]
+        for r, (n, before) in enumerate(zip(portions, histories)):
+            positions += list(range(before, before + n))
+            owner += [r] * n
+            starts.append(starts[-1] + n)
+        return StepContext(tokens=len(positions), requests=len(portions),
+                           token_ids=ints([0] * len(positions)), positions=ints(positions),
+                           token_request=ints(owner), request_start=ints(starts),
+                           history=ints(histories), max_portion=max(portions),
+                           max_context=max(p + h for p, h in zip(portions, histories)))
+
+    def entry(seconds, moved=None, flops=None):
+        out = {"us": round(seconds * 1e6, 2)}
+        if moved is not None:
+            out["gbs"] = round(moved / seconds / 1e9, 1)
+            out["hbm_frac"] = round(moved / seconds / 1e9 / peak["hbm_gbs"], 4)
+        if flops is not None:
+            out["tflops"] = round(flops / seconds / 1e12, 2)
+            out["tensor_frac"] = round(flops / seconds / 1e12 / peak["bf16_tflops"], 4)
+        return out
+
+    out = {}
+    for label, portions, histories in (("decode", [1] * batch, [2048] * batch),
+                                       ("prefill", [PREFILL_TOKENS], [0])):
+        ctx = ctx_of(portions, histories)
+        tokens, requests = ctx.tokens, ctx.requests
+        # ---- the state space beside lightning attention, equal state sizes
+        H, P, N = width // 64, 64, 128
+        state_size = H * N * P
+        copies = max(2, min(24, int(200e6 // (requests * state_size * 4))))
+        state = torch.zeros(copies * requests, state_size, device=device)
+        views = [StateView(state, ints(list(range(c * requests, (c + 1) * requests))),
+                           FixedState((state_size,), "float32")) for c in range(copies)]
+        channels = H * P + 2 * N
+        mixed = [bf16(tokens, channels) for _ in range(copies)]
+        raw = [bf16(tokens, H) for _ in range(copies)]
+        constants = dict(a_log=torch.full((H,), -3.0, device=device),
+                         dt_bias=torch.zeros(H, device=device), skip=torch.ones(H, device=device),
+                         ctx=ctx, write=True, heads=H, value_dim=P, state_dim=N, groups=1)
+        seconds = graph_seconds(lambda i: ops.state_space_scan(mixed[i], raw[i], view=views[i],
+                                                               **constants), copies, 2 * copies)
+        moved = tokens * ((channels + H) * 2 + H * P * 4) + 2 * requests * state_size * 4
+        out[f"{label}_state_space"] = entry(seconds, moved)
+        out[f"{label}_state_space"]["gflops_fma"] = round(4.0 * tokens * H * N * P / seconds / 1e9, 1)
+        LH, D, V = width // 128, 128, 128
+        wide = 2 * LH * D + 2 * LH * V
+        projected = [bf16(tokens, wide) for _ in range(copies)]
+        decay = torch.full((LH,), 0.97, device=device)
+        weight = torch.ones(LH * V, device=device)
+        seconds = graph_seconds(lambda i: ops.lightning_attention(
+            projected[i], decay=decay, norm_weight=weight, eps=1e-6, ctx=ctx, view=views[i],
+            write=True, heads=LH, key_dim=D, value_dim=V), copies, 2 * copies)
+        moved = tokens * (wide + LH * V) * 2 + 2 * requests * state_size * 4
+        out[f"{label}_lightning_farorax"] = entry(seconds, moved)
+        out[f"{label}_lightning_farorax"]["gflops_fma"] = round(4.0 * tokens * LH * D * V / seconds / 1e9, 1)
+        # ---- the convolution ahead of the state space; the gate and norm behind it
+        taps = 4
+        slots = torch.zeros(copies * requests, taps - 1, channels, device=device).bfloat16()
+        conv_views = [StateView(slots, views[c].slots, FixedState((taps - 1, channels)))
+                      for c in range(copies)]
+        kernel, bias = torch.randn(channels, taps, device=device), torch.zeros(channels, device=device)
+        seconds = graph_seconds(lambda i: ops.channel_conv(mixed[i], kernel, bias, taps=taps,
+                                                           activation="silu", ctx=ctx,
+                                                           view=conv_views[i], write=True),
+                                copies, 2 * copies)
+        out[f"{label}_channel_conv"] = entry(seconds, tokens * channels * 4 +
+                                             2 * requests * (taps - 1) * channels * 2)
+        y = [torch.randn(tokens, H * P, device=device) for _ in range(copies)]
+        gate = [bf16(tokens, H * P) for _ in range(copies)]
+        norm_weight = torch.ones(H * P, device=device)
+        seconds = graph_seconds(lambda i: ops.gated_group_norm(y[i], gate[i], norm_weight,
+                                                               groups=max(width // 256, 1), eps=1e-6,
+                                                               dtype=torch.bfloat16), copies, 2 * copies)
+        out[f"{label}_gated_group_norm"] = entry(seconds, tokens * H * P * (4 + 2 + 2))
+        del state, views, mixed, raw, projected, slots, conv_views, y, gate
+        # ---- attention over a window that keeps the first tokens beside a window alone
+        heads, kv_heads, head, window, keep = width // 64, width // 256, 64, 1024, 4
+        pages = -(-(histories[0] + portions[0]) // PAGE_SIZE)
+        table = ints([[r * pages + b for b in range(pages)] for r in range(requests)])
+        kv = (torch.randn(2, requests * pages + 1, kv_heads, PAGE_SIZE, head, device=device) * 0.3).bfloat16()
+        q = [bf16(tokens, heads, head) for _ in range(4)]
+        seen = sum(min(h + i + 1, window) for n, h in zip(portions, histories) for i in range(n))
+        moved = requests * min(histories[0] + portions[0], window + portions[0]) * kv_heads * head * 2 * 2 \
+            + tokens * heads * head * 2 * 2
+        flops = 4.0 * heads * head * seen
+        for name, kept in (("attention_kept_first", keep), ("attention_window_farorax", 0)):
+            view = PagedView(kv, table, PAGE_SIZE, PagedKeyValues(kv_heads, head, window, keep_first=kept))
+            seconds = graph_seconds(lambda i: ops.paged_attention(
+                q[i], heads=heads, kv_heads=kv_heads, head_dim=head, scale=0.125, window=window,
+                keep_first=kept, ctx=ctx, view=view), 4, 8)
+            out[f"{label}_{name}"] = entry(seconds, moved, flops)
+        mixed_heads = [bf16(tokens, heads * head) for _ in range(4)]
+        gates = [bf16(tokens, heads * head) for _ in range(4)]
+        seconds = graph_seconds(lambda i: ops.gate_heads(mixed_heads[i], gates[i], heads=heads,
+                                                         row_dim=head, value_dim=head, per_head=False), 4, 8)
+        out[f"{label}_gate_heads"] = entry(seconds, tokens * heads * head * 6)
+        del kv, q, mixed_heads, gates
+        # ---- the routed feed-forward with softmax scores, identity outputs and a gated shared
+        # expert beside Farorax's
+        experts, top, identity, ff, shared = 8, 3, 2, width, width
+        copies = max(2, min(12, int(300e6 // ((experts * ff + shared) * width * 6))))
+        stack = experts * ff + shared
+        gate_up = [bf16(2 * stack, width) * 0.02 for _ in range(copies)]
+        down = [bf16(width, stack) * 0.02 for _ in range(copies)]
+        x = bf16(tokens, width)
+        at = experts * ff
+        alone = [(torch.cat([g[at:at + shared], g[stack + at:stack + at + shared]]).contiguous(),
+                  d[:, at:].contiguous()) for g, d in zip(gate_up, down)]
+        router = torch.randn(experts + identity + 1, width, device=device)
+        correction = torch.zeros(experts + identity, device=device)
+
+        def routed(i):                  # what the routed feed-forward part runs
+            weights, others = ops.route_general(x, router, correction, experts=experts,
+                                                identity=identity, top=top, scores="softmax",
+                                                normalize=False, shared_gate=True)
+            if ops.sorts_experts(x, experts=experts, width=ff, top=top, stack=stack):
+                y = ops.routed_experts_sorted(x, weights, gate_up[i], down[i], experts=experts,
+                                              width=ff, top=top, shared_gate_up=alone[i][0],
+                                              shared_down=alone[i][1], shared_scale=others[1])
+            else:
+                gated = ops.linear_swiglu(x, gate_up[i])
+                ops.scale_expert_columns(gated, weights, ff)
+                ops.scale_expert_columns(gated[:, at:], others[1].view(-1, 1), shared)
+                y = ops.linear(gated, down[i])
+            ops.add_scaled_rows(y, x, others[0])
+            return y
+
+        def routed_farorax(i):
+            weights = ops.route_experts(x, router[:experts], experts=experts, top=2, groups=4,
+                                        keep=2, group_score=2)
+            if ops.sorts_experts(x, experts=experts, width=ff, top=2, stack=stack):
+                return ops.routed_experts_sorted(x, weights, gate_up[i], down[i], experts=experts,
+                                                 width=ff, top=2, shared_gate_up=alone[i][0],
+                                                 shared_down=alone[i][1])
+            gated = ops.linear_swiglu(x, gate_up[i])
+            ops.scale_expert_columns(gated, weights, ff)
+            return ops.linear(gated, down[i])
+        router_f = router[:experts].contiguous()
+        for name, fn, used in (("routed_ff", routed, 2.4 * ff + shared),
+                               ("routed_ff_farorax", routed_farorax, 2 * ff + shared)):
+            if name.endswith("farorax"):
+                router = router_f
+            seconds = graph_seconds(fn, copies, 2 * copies)
+            touched = min(experts, tokens * 3) * ff + shared
+            out[f"{label}_{name}"] = entry(seconds, touched * width * 6 if label == "decode" else None,
+                                           6.0 * tokens * used * width if label == "prefill" else None)
+        del gate_up, down
+        # ---- the norm of a part's output added into the stream beside add + norm
+        residual = [torch.zeros(tokens, width, device=device) for _ in range(4)]
+        delta = [bf16(tokens, width) for _ in range(4)]
+        vector = torch.ones(width, device=device)
+        seconds = graph_seconds(lambda i: ops.normed_mean_add(residual[i], [delta[i]], [vector], 1e-6), 4, 8)
+        out[f"{label}_output_norm_add"] = entry(seconds, tokens * width * (4 + 4 + 2))
+        seconds = graph_seconds(lambda i: ops.add_rmsnorm(residual[i], delta[i], vector, 1e-6,
+                                                          torch.bfloat16), 4, 8)
+        out[f"{label}_add_rmsnorm_farorax"] = entry(seconds, tokens * width * (4 + 4 + 2 + 2))
+        del residual, delta
+        torch.cuda.empty_cache()
+    return out
+
+
+def case_tirudra(args) -> int:
+    """Tirudra beside Farorax (the closest of the engine's models: a recurrent mixer with a matrix
+    state per head, softmax attention over a window, routed experts with a shared one) at equal
+    width, depth and vocabulary, random weights: decode tokens/s at ``--batch`` and ``--context``
+    (device-timed graph replays of the engine's step), prefill tokens/s of one 2,048-token prompt,
+    each against its bound, and the new kernels alone."""
+    import gc
+
+    import torch
+
+    peak = peaks()
+    warmup, steps = max(args.warmup, 3), min(args.steps, 128)
+    context = args.context or 2048
+    layers = min(args.layers, 8)
+    results = {}
+    for width in (1024, 2048):
+        for label, data in ((f"tirudra_w{width}", tirudra_shape(width, layers)),
+                            (f"farorax_w{width}", farorax_shape(width, layers))):
+            engine = engine_of(data, args.batch, context, warmup + steps, f"random-{label}")
+            model, spec = engine.model, engine.model.spec
+            weight_bytes = model.weight_bytes()
+            kv_per_token = engine.cache_bytes_per_token()
+            state_bytes = sum(g.storage[:, 0].numel() * g.storage.element_size()
+                              for g in engine.cache.states)
+            seconds, _, mean_context, launches = time_decode(engine, args.batch, context, warmup,
+                                                             steps, seed=3)
+            step_bytes = weight_bytes + args.batch * (mean_context * kv_per_token + 2 * state_bytes)
+            prefill_seconds = time_prefill(engine, PREFILL_TOKENS, 2, 3, seed=5)
+            flops = model_flops(spec, PREFILL_TOKENS)
+            results[label] = {
+                "layers": layers, "weight_mb": round(weight_bytes / 1e6, 1),
+                "state_mb_per_request": round(state_bytes / 1e6, 2),
+                "decode_tokens_per_s": round(args.batch * steps / seconds, 1),
+                "decode_ms_per_step": round(seconds / steps * 1e3, 4),
+                "decode_hbm_frac": round(step_bytes / (seconds / steps) / 1e9 / peak["hbm_gbs"], 4),
+                "launches_per_step": launches,
+                "prefill_tokens_per_s": round(PREFILL_TOKENS / prefill_seconds, 1),
+                "prefill_ms": round(prefill_seconds * 1e3, 3),
+                "prefill_tensor_frac": round(flops / prefill_seconds / (peak["bf16_tflops"] * 1e12), 4)}
+            del engine, model
+            gc.collect()
+            torch.cuda.empty_cache()
+        results[f"kernels_w{width}"] = tirudra_kernels(width, args.batch, peak)
+    print(json.dumps({"case": "tirudra", "batch": args.batch, "context": context, "steps": steps,
+                      "warmup": warmup, "dtype": "bf16", "peaks": peak["source"],
+                      "data": "synthetic: random weights, seeded uniform-random token ids",
+                      "results": results}))
+    return 0
+
+
 # --------------------------------------------------------------------------- Lamisun beside LFM2
 
 
@@ -1780,7 +2040,7 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--context", type=int, default=None,
                         help="context length (default 4096; --case long: prompt tokens, 32768)")
-    parser.add_argument("--case", default="decode", choices=["decode", "batching", "long", "galarax", "farorax", "lamisun"],
+    parser.add_argument("--case", default="decode", choices=["decode", "batching", "long", "galarax", "farorax", "lamisun", "tirudra"],
                         help="decode: the default line; batching: 128 requests batched "
                              "continuously (LFM2-700M shape); long: 4 x 32,768 tokens "
                              "(LFM2-350M shape)")
@@ -1815,6 +2075,8 @@ def main() -> int:
         return case_farorax(args)
     if args.case == "lamisun":
         return case_lamisun(args)
+    if args.case == "tirudra":
+        return case_tirudra(args)
     args.context = args.context or 4096
     if args.kernel:
         return kernel_case(args.kernel, args.batch, args.context)

@@ -10,7 +10,7 @@ from dataclasses import asdict
 import click
 
 
-@click.group(help="B200-native inference engine (LFM2, Galarax, Farorax and Lamisun models).")
+@click.group(help="B200-native inference engine (LFM2, Galarax, Farorax, Lamisun and Tirudra models).")
 def main() -> None:
     pass
 

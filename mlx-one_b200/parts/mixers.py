@@ -64,13 +64,15 @@ class Attention(Mixer):
         hd, vd, _ = cls._sizes(spec)
         q_dim, k_dim, v_dim = spec["heads"] * hd, spec["kv_heads"] * hd, spec["kv_heads"] * vd
         own_values = cls._own_values(spec)
+        # (stored tensors keep their order from version to version: weights drawn in order by a
+        # seeded generator stay what they were)
         out = {
             "q_proj.weight": TensorSpec((q_dim, hidden)),
             "k_proj.weight": TensorSpec((k_dim, hidden)),
-            "out_proj.weight": TensorSpec((hidden, spec["heads"] * vd)),
         }
         if own_values:
             out["v_proj.weight"] = TensorSpec((v_dim, hidden))
+        out["out_proj.weight"] = TensorSpec((hidden, spec["heads"] * vd))
         if spec.get("bias"):
             out["q_proj.bias"] = TensorSpec((q_dim,), "bias")
             out["k_proj.bias"] = TensorSpec((k_dim,), "bias")
