@@ -252,10 +252,20 @@ struct Item {
     int q_token;            // first token of the tile among all tokens of the step
     int tokens_here;        // tokens of the tile that belong to the portion
     int first_position;     // position of the first token in its request
-    int tile_first;         // first key tile (of this item's split)
+    int tile_first;         // first key tile of the window's run (of this item's split)
     int tile_count;         // 0: a split without keys (it only reports that it saw none)
     int split;
+    // Behind a window the sequence's first positions may stay visible: their key tiles are walked
+    // first, `kept_tiles` of them from tile `kept_first` on, then tile_count - kept_tiles tiles
+    // from `tile_first` on.
+    int kept_first;
+    int kept_tiles;
 };
+
+// the place among the keys of the j-th tile that an item walks
+__device__ __forceinline__ int tile_of(const Item& item, int j) {
+    return j < item.kept_tiles ? item.kept_first + j : item.tile_first + j - item.kept_tiles;
+}
 
 template <int KEYS, int PARTS>
 __global__ void __launch_bounds__((4 * PARTS + 2) * 32, Shape<KEYS>::BLOCKS_PER_SM)
@@ -266,7 +276,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                          const int* __restrict__ history, bf16* __restrict__ out, int requests,
                          int heads, int kv_heads, float scale_log2, int window, int token_tiles,
                          int splits, float* __restrict__ partial, const float* __restrict__ sinks,
-                         int* __restrict__ error_flag) {
+                         int* __restrict__ error_flag, int keep_first) {
     using S = Shape<KEYS>;
     constexpr int COPY_WARP = 4 * PARTS, MMA_WARP = 4 * PARTS + 1;
     constexpr int THREADS = (4 * PARTS + 2) * 32;     // softmax warps, the copy warp, the product warp
@@ -315,13 +325,17 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                 const int last_position = item.first_position + item.tokens_here - 1;
                 const int lowest = first_visible_key(item.first_position, window);
                 item.tile_first = lowest / KEYS;
-                item.tile_count = last_position / KEYS - item.tile_first + 1;
-                if (splits > 1) {
-                    const int share = (item.tile_count + splits - 1) / splits;
-                    const int end = item.tile_first + item.tile_count;
-                    item.tile_first += item.split * share;
-                    item.tile_count = max(min(share, end - item.tile_first), 0);
-                }
+                // the kept first positions' tiles that lie wholly ahead of the window's first
+                const int kept = min((min(keep_first, lowest) + KEYS - 1) / KEYS, item.tile_first);
+                const int walked = kept + last_position / KEYS - item.tile_first + 1;
+                // this split's share [from, to) of the tiles in the order they are walked
+                const int share = (walked + splits - 1) / splits;
+                const int from = splits > 1 ? item.split * share : 0;
+                const int to = splits > 1 ? min(from + share, walked) : walked;
+                item.kept_first = from;
+                item.kept_tiles = max(min(to, kept) - from, 0);
+                item.tile_first += max(from, kept) - kept;
+                item.tile_count = max(to - from, 0);
                 break;
             }
             left -= tiles;
@@ -404,8 +418,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
             // may see its keys
             auto box_row = [&](int j) {
                 long long row = -1;
-                const int key = (item.tile_first + j) * KEYS + lane * box_keys;
-                if (lane < boxes && key <= last_position && key + box_keys - 1 >= lowest) {
+                const int key = tile_of(item, j) * KEYS + lane * box_keys;
+                if (lane < boxes && key <= last_position &&
+                    (key + box_keys - 1 >= lowest || key < keep_first)) {
                     const int block = key / page_size;
                     const int page = block < table_width ? table[block] : -1;
                     if (page >= 0)
@@ -554,7 +569,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                 return true;
             };
             for (int j = 0; j < item.tile_count && ok; ++j, ++t) {
-                const int tile_key = (item.tile_first + j) * KEYS;
+                const int tile_key = tile_of(item, j) * KEYS;
                 const int key0 = tile_key + part * MY_KEYS;
                 ok = barrier_wait(s_ready(t & 1), (t >> 1) & 1, error_flag);
                 if (!ok) break;
@@ -566,7 +581,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                 if (!open) {
 #pragma unroll
                     for (int i = 0; i < MY_KEYS; ++i)
-                        if (!(key0 + i >= limit_lo && key0 + i <= limit_hi)) v[i] = -INFINITY;
+                        if (!((key0 + i >= limit_lo || key0 + i < keep_first) && key0 + i <= limit_hi))
+                            v[i] = -INFINITY;
                 }
                 float tops[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
@@ -763,14 +779,16 @@ MLXONE_API int mlxone_attention_tcgen05_splits(int tokens, int requests, int hea
 // splits > 1 (with partial, see mlxone_attention_tcgen05_splits): the items are cut by keys and
 // `out` is left for the merge to write. `sinks` (float32 [heads] or null): exp(sink) of a query's
 // head stands in the denominator of its softmax beside the keys' terms.
-MLXONE_API int mlxone_attention_prefill_tcgen05(const void* q, const void* kv, const int* block_table,
+static int prefill_tcgen05(const void* q, const void* kv, const int* block_table,
                                                 int table_width, int page_size, int pages,
                                                 const int* request_start, const int* history,
                                                 void* out, int tokens, int requests, int heads,
                                                 int kv_heads, int head_dim, float scale, int window,
                                                 int splits, float* partial, const float* sinks,
-                                                int* error_flag, cudaStream_t stream) {
+                                                int* error_flag, cudaStream_t stream, int keep_first) {
     if (tokens == 0) return 0;
+    MLXONE_REQUIRE(keep_first >= 0 && (keep_first == 0 || window > 0),
+                   "attention_prefill_tcgen05: first positions are kept behind a window only");
     MLXONE_REQUIRE(tokens > 0 && requests > 0, "attention_prefill_tcgen05: bad sizes");
     MLXONE_REQUIRE(supported(head_dim, heads, kv_heads, page_size),
                    "attention_prefill_tcgen05: head size %d, %d heads over %d key heads and pages of "
@@ -847,7 +865,34 @@ MLXONE_API int mlxone_attention_prefill_tcgen05(const void* q, const void* kv, c
     kernel<<<dim3((unsigned)blocks), threads, shared, stream>>>(
         map_q, map_kv, value_rows, block_table, table_width, page_size, box_keys, request_start,
         history, static_cast<bf16*>(out), requests, heads, kv_heads, scale * 1.4426950408889634f,
-        window, token_tiles, splits, partial, sinks, error_flag);
+        window, token_tiles, splits, partial, sinks, error_flag, keep_first);
     MLXONE_LAUNCH_CHECK("attention_prefill_tcgen05");
     return 0;
+}
+
+MLXONE_API int mlxone_attention_prefill_tcgen05(const void* q, const void* kv, const int* block_table,
+                                                int table_width, int page_size, int pages,
+                                                const int* request_start, const int* history,
+                                                void* out, int tokens, int requests, int heads,
+                                                int kv_heads, int head_dim, float scale, int window,
+                                                int splits, float* partial, const float* sinks,
+                                                int* error_flag, cudaStream_t stream) {
+    return prefill_tcgen05(q, kv, block_table, table_width, page_size, pages, request_start, history,
+                           out, tokens, requests, heads, kv_heads, head_dim, scale, window, splits,
+                           partial, sinks, error_flag, stream, 0);
+}
+
+// ... with a window behind which the first `keep_first` positions of a sequence stay visible
+MLXONE_API int mlxone_attention_prefill_tcgen05_keep(const void* q, const void* kv,
+                                                     const int* block_table, int table_width,
+                                                     int page_size, int pages,
+                                                     const int* request_start, const int* history,
+                                                     void* out, int tokens, int requests, int heads,
+                                                     int kv_heads, int head_dim, float scale,
+                                                     int window, int keep_first, int splits,
+                                                     float* partial, const float* sinks,
+                                                     int* error_flag, cudaStream_t stream) {
+    return prefill_tcgen05(q, kv, block_table, table_width, page_size, pages, request_start, history,
+                           out, tokens, requests, heads, kv_heads, head_dim, scale, window, splits,
+                           partial, sinks, error_flag, stream, keep_first);
 }

@@ -1298,24 +1298,14 @@ class CudaOps:
             rest = ctx.requests - singles
             table = view.block_table[singles:]
             starts, history = ctx.request_start[singles:], ctx.history[singles:]
-            if keep_first:
-                # (the tcgen05 kernel walks one run of key tiles; the kept first positions are a
-                # second run, which the mma.sync kernel takes)
-                self._call("mlxone_attention_prefill_keep", _c_void_p(_ptr(q)),
-                           _c_void_p(_ptr(view.kv)), _c_void_p(_ptr(table)),
-                           _c_int(width), _c_int(view.page_size), _c_int(pages),
-                           _c_void_p(_ptr(starts)), _c_void_p(_ptr(history)),
-                           _c_void_p(_ptr(out)), _c_int(tokens), _c_int(rest),
-                           _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_float(scale),
-                           _c_int(window), _c_int(keep_first), _c_void_p(_ptr(sinks)))
-            elif (self.tcgen05_attention and q.dtype == torch.bfloat16
+            if (self.tcgen05_attention and q.dtype == torch.bfloat16
                     and self.lib.mlxone_attention_tcgen05_supports(
                         _c_int(head_dim), _c_int(heads), _c_int(kv_heads), _c_int(view.page_size))):
                 # few query tiles (a prompt's portion beside a step's decodes): their keys are
                 # cut into parts that run side by side, and a merge follows
                 bound = min(ctx.max_context, width * view.page_size)
                 if window:
-                    bound = min(bound, abs(window) + ctx.max_portion)
+                    bound = min(bound, abs(window) + ctx.max_portion + keep_first)
                 splits = 1
                 if self.prefill_key_splits:
                     splits = self.lib.mlxone_attention_tcgen05_splits(
@@ -1325,14 +1315,15 @@ class CudaOps:
                 if splits > 1:
                     partial = torch.empty(tokens * heads * splits * (head_dim + 2),
                                           dtype=torch.float32, device=self.device)
-                self._call("mlxone_attention_prefill_tcgen05", _c_void_p(_ptr(q)),
+                self._call("mlxone_attention_prefill_tcgen05_keep", _c_void_p(_ptr(q)),
                            _c_void_p(_ptr(view.kv)), _c_void_p(_ptr(table)),
                            _c_int(width), _c_int(view.page_size), _c_int(pages),
                            _c_void_p(_ptr(starts)), _c_void_p(_ptr(history)),
                            _c_void_p(_ptr(out)), _c_int(tokens), _c_int(rest),
                            _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_float(scale),
-                           _c_int(window or 0), _c_int(splits), _c_void_p(_ptr(partial)),
-                           _c_void_p(_ptr(sinks)), _c_void_p(_ptr(self.error_flag)))
+                           _c_int(window or 0), _c_int(keep_first), _c_int(splits),
+                           _c_void_p(_ptr(partial)), _c_void_p(_ptr(sinks)),
+                           _c_void_p(_ptr(self.error_flag)))
                 if partial is not None:
                     # (the leading single tokens are the decode kernel's: their rows stay)
                     skip = singles * heads * splits * (head_dim + 2)
@@ -1340,13 +1331,13 @@ class CudaOps:
                                _c_void_p(_ptr(out[singles:])), _c_int((tokens - singles) * heads),
                                _c_int(splits), _c_int(head_dim))
             else:
-                self._call("mlxone_attention_prefill", _c_void_p(_ptr(q)),
+                self._call("mlxone_attention_prefill_keep", _c_void_p(_ptr(q)),
                            _c_void_p(_ptr(view.kv)), _c_void_p(_ptr(table)),
                            _c_int(width), _c_int(view.page_size), _c_int(pages),
                            _c_void_p(_ptr(starts)), _c_void_p(_ptr(history)),
                            _c_void_p(_ptr(out)), _c_int(tokens), _c_int(rest),
                            _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_float(scale),
-                           _c_int(window or 0), _c_void_p(_ptr(sinks)))
+                           _c_int(window or 0), _c_int(keep_first), _c_void_p(_ptr(sinks)))
             return out
         self._call("mlxone_attention_generic", _c_void_p(_ptr(q)), _c_void_p(_ptr(view.kv)),
                    _c_void_p(_ptr(view.block_table)), _c_int(width),
