@@ -72,9 +72,15 @@ channel_conv_kernel(const T* __restrict__ rows, int ld, const float* __restrict_
 }
 
 // The same, 16 bytes of channels a thread (8 bfloat16 or 4 float), for channel counts, row
-// strides and addresses that allow it: every tap is one 16-byte load.
+// strides and addresses that allow it and up to WIDE_TAPS taps: a thread keeps its channels'
+// weights in registers over a run of WIDE_TOKENS tokens, and every tap of a token is one 16-byte
+// load.
+constexpr int WIDE_THREADS = 64;
+constexpr int WIDE_TOKENS = 8;
+constexpr int WIDE_TAPS = 8;
+
 template <typename T>
-__global__ void __launch_bounds__(CONV_THREADS)
+__global__ void __launch_bounds__(WIDE_THREADS)
 channel_conv_wide_kernel(const T* __restrict__ rows, int ld, const float* __restrict__ kernel,
                          const float* __restrict__ bias, const T* __restrict__ state,
                          const int* __restrict__ slots, const int* __restrict__ token_request,
@@ -82,38 +88,49 @@ channel_conv_wide_kernel(const T* __restrict__ rows, int ld, const float* __rest
                          T* __restrict__ out, int tokens, int channels, int taps, int activation) {
     constexpr int V = 16 / sizeof(T);
     griddep_launch();
-    griddep_wait();
-    const int groups = channels / V;
-    const long long i = (long long)blockIdx.x * CONV_THREADS + threadIdx.x;
-    if (i >= (long long)tokens * groups) return;
-    const int t = (int)(i / groups), c = (int)(i - (long long)t * groups) * V;
-    const int r = token_request[t];
-    const int first = request_start[r];
-    const int before = history[r];
-    float sum[V];
+    const int group = blockIdx.x * WIDE_THREADS + threadIdx.x;
+    if (group >= channels / V) return;
+    const int c = group * V;
+    float w[V][WIDE_TAPS], b[V];
 #pragma unroll
-    for (int v = 0; v < V; ++v) sum[v] = bias != nullptr ? bias[c + v] : 0.f;
-    for (int j = 0; j < taps; ++j) {
-        const int source = t - (taps - 1 - j);
-        const T* from = nullptr;
-        if (source >= first) {
-            from = rows + (size_t)source * ld + c;
-        } else if (state != nullptr) {
-            const int row = taps - 1 - (first - source);
-            if (row >= 0 && before - (first - source) >= 0)
-                from = state + ((size_t)slots[r] * (taps - 1) + row) * channels + c;
-        }
-        if (from == nullptr) continue;
-        const uint4 packed = *reinterpret_cast<const uint4*>(from);
-        const T* u = reinterpret_cast<const T*>(&packed);
+    for (int v = 0; v < V; ++v) {
+        b[v] = bias != nullptr ? bias[c + v] : 0.f;
 #pragma unroll
-        for (int v = 0; v < V; ++v) sum[v] = fmaf(kernel[(size_t)(c + v) * taps + j], to_float<T>(u[v]), sum[v]);
+        for (int j = 0; j < WIDE_TAPS; ++j) w[v][j] = j < taps ? kernel[(size_t)(c + v) * taps + j] : 0.f;
     }
-    uint4 packed;
-    T* y = reinterpret_cast<T*>(&packed);
+    griddep_wait();
+    const int stop = min(tokens, (int)(blockIdx.y + 1) * WIDE_TOKENS);
+    for (int t = blockIdx.y * WIDE_TOKENS; t < stop; ++t) {
+        const int r = token_request[t];
+        const int first = request_start[r];
+        const int before = history[r];
+        float sum[V];
 #pragma unroll
-    for (int v = 0; v < V; ++v) y[v] = from_float<T>(activation == 1 ? silu(sum[v]) : sum[v]);
-    *reinterpret_cast<uint4*>(out + (size_t)t * channels + c) = packed;
+        for (int v = 0; v < V; ++v) sum[v] = b[v];
+#pragma unroll
+        for (int j = 0; j < WIDE_TAPS; ++j) {
+            if (j >= taps) continue;
+            const int source = t - (taps - 1 - j);
+            const T* from = nullptr;
+            if (source >= first) {
+                from = rows + (size_t)source * ld + c;
+            } else if (state != nullptr) {
+                const int row = taps - 1 - (first - source);
+                if (row >= 0 && before - (first - source) >= 0)
+                    from = state + ((size_t)slots[r] * (taps - 1) + row) * channels + c;
+            }
+            if (from == nullptr) continue;
+            const uint4 packed = *reinterpret_cast<const uint4*>(from);
+            const T* u = reinterpret_cast<const T*>(&packed);
+#pragma unroll
+            for (int v = 0; v < V; ++v) sum[v] = fmaf(w[v][j], to_float<T>(u[v]), sum[v]);
+        }
+        uint4 packed;
+        T* y = reinterpret_cast<T*>(&packed);
+#pragma unroll
+        for (int v = 0; v < V; ++v) y[v] = from_float<T>(activation == 1 ? silu(sum[v]) : sum[v]);
+        *reinterpret_cast<uint4*>(out + (size_t)t * channels + c) = packed;
+    }
 }
 
 // after a step with portions: the slot's rows become the last taps - 1 inputs (one thread per
@@ -373,6 +390,32 @@ int dispatch_scan(const ScanArgs& a, int requests, int max_portion, cudaStream_t
 
 constexpr int NORM_THREADS = 256;
 
+// a block per (token, part), for steps of few tokens
+template <typename T>
+__global__ void __launch_bounds__(NORM_THREADS)
+gated_group_norm_block_kernel(const float* __restrict__ y, const T* __restrict__ gate, int ld,
+                              const float* __restrict__ weight, T* __restrict__ out, int inner,
+                              int groups, float eps) {
+    __shared__ float scratch[33];
+    griddep_launch();
+    griddep_wait();
+    const int t = blockIdx.x, part = blockIdx.y;
+    const int size = inner / groups;
+    const float* row = y + (size_t)t * inner + (size_t)part * size;
+    const T* z = gate + (size_t)t * ld + (size_t)part * size;
+    float squares = 0.f;
+    for (int c = threadIdx.x; c < size; c += NORM_THREADS) {
+        const float v = row[c] * silu(to_float<T>(z[c]));
+        squares = fmaf(v, v, squares);
+    }
+    const float inverse = rsqrtf(block_sum(squares, scratch) / (float)size + eps);
+    for (int c = threadIdx.x; c < size; c += NORM_THREADS) {
+        const float v = row[c] * silu(to_float<T>(z[c]));
+        out[(size_t)t * inner + (size_t)part * size + c] =
+            from_float<T>(v * inverse * weight[(size_t)part * size + c]);
+    }
+}
+
 // a warp per (token, part): up to KEPT values a lane stay in registers between the sum of squares
 // and the output (parts of up to 32 * KEPT values; longer parts are read twice)
 template <typename T>
@@ -450,12 +493,13 @@ MLXONE_API int mlxone_channel_conv(const void* rows, int ld, const float* kernel
         } else {                                                                                   \
             constexpr int V = 16 / sizeof(T);                                                      \
             const bool wide = channels % V == 0 && ld % V == 0 && (uintptr_t)rows % 16 == 0 &&     \
-                              (uintptr_t)out % 16 == 0 && (uintptr_t)state % 16 == 0;              \
+                              (uintptr_t)out % 16 == 0 && (uintptr_t)state % 16 == 0 &&            \
+                              taps <= WIDE_TAPS && tokens <= 65535 * WIDE_TOKENS;                  \
             if (wide)                                                                              \
                 e = launch_kernel(channel_conv_wide_kernel<T>,                                     \
-                                  dim3(ceil_div_host((long long)tokens * (channels / V),           \
-                                                     CONV_THREADS)),                               \
-                                  dim3(CONV_THREADS), 0, stream, true, (const T*)rows, ld, kernel, \
+                                  dim3(ceil_div_host(channels / V, WIDE_THREADS),                  \
+                                       ceil_div_host(tokens, WIDE_TOKENS)),                        \
+                                  dim3(WIDE_THREADS), 0, stream, true, (const T*)rows, ld, kernel, \
                                   bias, (const T*)state, slots, token_request, request_start,      \
                                   history, (T*)out, tokens, channels, taps, activation);           \
             else                                                                                   \
@@ -515,7 +559,18 @@ MLXONE_API int mlxone_gated_group_norm(const float* y, const void* gate, int ld,
     cudaError_t e;
     const long long items = (long long)tokens * groups;
     const dim3 grid(ceil_div_host(items, NORM_THREADS / 32));
-    if (dtype == MLXONE_BF16)
+    // few tokens: a block per part (the step is bound by latency, and 256 threads a part have the
+    // shorter chain); many: a warp per part (no barriers, values kept in registers)
+    if (items < 1024 && groups <= 65535) {
+        if (dtype == MLXONE_BF16)
+            e = launch_kernel(gated_group_norm_block_kernel<__nv_bfloat16>, dim3(tokens, groups),
+                              dim3(NORM_THREADS), 0, stream, true, y, (const __nv_bfloat16*)gate, ld,
+                              weight, (__nv_bfloat16*)out, inner, groups, eps);
+        else
+            e = launch_kernel(gated_group_norm_block_kernel<float>, dim3(tokens, groups),
+                              dim3(NORM_THREADS), 0, stream, true, y, (const float*)gate, ld, weight,
+                              (float*)out, inner, groups, eps);
+    } else if (dtype == MLXONE_BF16)
         e = launch_kernel(gated_group_norm_kernel<__nv_bfloat16>, grid, dim3(NORM_THREADS), 0, stream,
                           true, y, (const __nv_bfloat16*)gate, ld, weight, (__nv_bfloat16*)out, inner,
                           groups, eps, items);
