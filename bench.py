@@ -1929,6 +1929,37 @@ def kernel_case(name: str, batch: int, context: int) -> int:
                          write=True, heads=heads, key_dim=key_dim, value_dim=value_dim)
         run = lambda i: ops.lightning_attention(rows[i % 4], view=views[i % 4], **constants)
         work = f"{ctx.tokens} tokens of {len(portions)} requests, {heads} heads of {key_dim} x {value_dim}, state {slot * 4 / 1e6:.1f} MB a request"
+    elif name in ("state_space_prefill", "state_space_decode", "channel_conv_prefill"):
+        # a selective state space at the shape of a 2048-wide model: one 2,048-token prompt
+        # (segments: build, chain, scan) or `batch` single tokens; and the convolution ahead of it
+        from mlx_one_b200.parts import FixedState, StateView
+
+        heads, value_dim, state_dim, taps = 32, 64, 128, 4
+        slot = heads * state_dim * value_dim
+        channels = heads * value_dim + 2 * state_dim
+        portions = [1] * batch if name == "state_space_decode" else [PREFILL_TOKENS]
+        ctx, _ = batch_context(portions, [context if name == "state_space_decode" else 0] * len(portions))
+        slots = [torch.arange(c * len(portions), (c + 1) * len(portions), dtype=torch.int32,
+                              device=device) for c in range(4)]
+        rows = [torch.randn(ctx.tokens, channels, device=device).bfloat16() for _ in range(4)]
+        if name == "channel_conv_prefill":
+            kept = torch.zeros(4 * len(portions), taps - 1, channels, device=device).bfloat16()
+            views = [StateView(kept, slots[c], FixedState((taps - 1, channels))) for c in range(4)]
+            kernel, bias = torch.randn(channels, taps, device=device), torch.zeros(channels, device=device)
+            run = lambda i: ops.channel_conv(rows[i % 4], kernel, bias, taps=taps, activation="silu",
+                                             ctx=ctx, view=views[i % 4], write=True)
+            work = f"{ctx.tokens} tokens, {channels} channels, {taps} taps"
+        else:
+            state = torch.zeros(4 * len(portions), slot, device=device)
+            views = [StateView(state, slots[c], FixedState((slot,), "float32")) for c in range(4)]
+            raw = [torch.randn(ctx.tokens, heads, device=device).bfloat16() for _ in range(4)]
+            constants = dict(a_log=torch.full((heads,), -3.0, device=device),
+                             dt_bias=torch.zeros(heads, device=device),
+                             skip=torch.ones(heads, device=device), ctx=ctx, write=True, heads=heads,
+                             value_dim=value_dim, state_dim=state_dim, groups=1)
+            run = lambda i: ops.state_space_scan(rows[i % 4], raw[i % 4], view=views[i % 4], **constants)
+            work = (f"{ctx.tokens} tokens of {len(portions)} requests, {heads} heads of {state_dim} x "
+                    f"{value_dim}, state {slot * 4 / 1e6:.1f} MB a request")
     elif name in ("latent_prefill", "latent_decode"):
         # attention over latent rows at the sizes of a Lamisun 1024 wide: one 2,048-token prompt
         # (the kernel whose warps own 16 rows) or `batch` single tokens (key runs and their merge)
@@ -2054,7 +2085,8 @@ def main() -> int:
                         help="run one kernel alone instead of the benchmark: skinny_swiglu, "
                              "skinny_in_proj, skinny_down, decode_attention, prefill_attention, tcgen05_swiglu, "
                              "swapped_swiglu, mixed_attention, sampling, delta_prefill, delta_decode, lightning_prefill, "
-                             "lightning_decode, experts_sorted, latent_prefill, latent_decode, decode_step (the "
+                             "lightning_decode, experts_sorted, latent_prefill, latent_decode, state_space_prefill, "
+                             "state_space_decode, channel_conv_prefill, decode_step (the "
                              "whole step, eager, for a launch list), decode_timeline (where "
                              "the graph-replayed step's time goes, kernel by kernel)")
     parser.add_argument("--dependent-launches", type=int, default=1,

@@ -12,8 +12,9 @@
 // output (compute dtype) and are used in 32-bit. A column of S depends on no other column: a
 // block holds 32 columns of one head of one request, its four warps every fourth row of them in
 // registers (a lane = a column, so the state moves 128 bytes at a time), and walks the request's
-// tokens of the step in order, eight at a time, with B, C (times dt where it enters the state),
-// the decays and the block's slice of x staged in shared memory. The four warps' shares of an
+// tokens of the step in order, eight at a time, with B, C, the step sizes, the decays and the
+// block's slice of x staged in shared memory (the next eight tokens' raw values are fetched into
+// registers meanwhile). The four warps' shares of an
 // output meet in shared memory in a fixed order, so a token's result does not depend on how the
 // tokens were cut into steps.
 //
@@ -99,8 +100,11 @@ channel_conv_wide_kernel(const T* __restrict__ rows, int ld, const float* __rest
         for (int j = 0; j < WIDE_TAPS; ++j) w[v][j] = j < taps ? kernel[(size_t)(c + v) * taps + j] : 0.f;
     }
     griddep_wait();
-    const int stop = min(tokens, (int)(blockIdx.y + 1) * WIDE_TOKENS);
-    for (int t = blockIdx.y * WIDE_TOKENS; t < stop; ++t) {
+    // (unrolled, so that the loads of all the run's tokens are on their way together)
+#pragma unroll
+    for (int k = 0; k < WIDE_TOKENS; ++k) {
+        const int t = blockIdx.y * WIDE_TOKENS + k;
+        if (t >= tokens) continue;
         const int r = token_request[t];
         const int first = request_start[r];
         const int before = history[r];
@@ -220,13 +224,13 @@ struct ScanArgs {
 // MODE 2: a segment from its incoming state in `carried` (segment 0: the slot's state, which the
 //         chaining pass has copied there); outputs; the last segment writes the slot.
 template <typename T, int NR, int MODE>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, NR <= 32 ? 4 : 2)
 state_space_scan_kernel(ScanArgs a) {
     constexpr int NPAD = LANES * NR;                 // rows covered (>= state_dim)
-    __shared__ float sb[TOK][NPAD];                  // dt * B
+    __shared__ float sb[TOK][NPAD];
     __shared__ float sc[TOK][NPAD];
     __shared__ float sx[TOK][COLS];
-    __shared__ float sdecay[TOK];
+    __shared__ float sdecay[TOK], sdt[TOK];
     __shared__ float partial[TOK][LANES][COLS];
     griddep_launch();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -267,35 +271,67 @@ state_space_scan_kernel(ScanArgs a) {
     float product = 1.f;
     const T* mixed = reinterpret_cast<const T*>(a.mixed);
     const T* steps = reinterpret_cast<const T*>(a.steps);
-    for (int base = first; base < last; base += TOK) {
+    // MODE 1 (no outputs, few registers): the raw values of the next eight tokens wait in
+    // registers while the present eight are worked on: this thread's share of B and C (PER values
+    // each), of the block's slice of x (two values) and, for the first threads, a token's step
+    // size. The other modes stage a group of tokens when they come to it: with the outputs' sums
+    // in flight too, the registers that fetching ahead takes cost more warps than the wait.
+    constexpr int PER = TOK * NPAD / THREADS;
+    T rb[PER], rc[PER], rx[TOK * COLS / THREADS], rdt;
+    auto fetch = [&](int base) {
         const int count = min(TOK, last - base);
-        __syncthreads();
-        if (threadIdx.x < count) {
-            const float dt = softplus(to_float<T>(steps[(size_t)(base + threadIdx.x) * a.ld_steps + head]) + bias);
-            sdecay[threadIdx.x] = expf(-rate * dt);
-            partial[threadIdx.x][0][0] = dt;           // (kept here until B is staged)
-        }
-        __syncthreads();
-        for (int i = threadIdx.x; i < count * NPAD; i += THREADS) {
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {
+            const int i = threadIdx.x + k * THREADS;
             const int t = i / NPAD, n = i - t * NPAD;
-            const T* row = mixed + (size_t)(base + t) * channels + inner + (size_t)group * N;
-            const float dt = partial[t][0][0];
-            sb[t][n] = n < N ? dt * to_float<T>(row[n]) : 0.f;
-            sc[t][n] = n < N ? to_float<T>(row[(size_t)a.groups * N + n]) : 0.f;
+            const bool have = t < count && n < N;
+            const T* row = mixed + (size_t)(base + (have ? t : 0)) * channels + inner + (size_t)group * N;
+            rb[k] = have ? row[n] : from_float<T>(0.f);
+            rc[k] = have ? row[(size_t)a.groups * N + n] : from_float<T>(0.f);
         }
-        for (int i = threadIdx.x; i < count * COLS; i += THREADS) {
+#pragma unroll
+        for (int k = 0; k < TOK * COLS / THREADS; ++k) {
+            const int i = threadIdx.x + k * THREADS;
             const int t = i / COLS, c = i - t * COLS;
             const int col = blockIdx.x * COLS + c;
-            sx[t][c] = col < P ? to_float<T>(mixed[(size_t)(base + t) * channels + (size_t)head * P + col]) : 0.f;
+            const bool have = t < count && col < P;
+            rx[k] = have ? mixed[(size_t)(base + t) * channels + (size_t)head * P + col] : from_float<T>(0.f);
+        }
+        rdt = threadIdx.x < count ? steps[(size_t)(base + threadIdx.x) * a.ld_steps + head]
+                                  : from_float<T>(0.f);
+    };
+    if (MODE == 1) fetch(first);
+    for (int base = first; base < last; base += TOK) {
+        const int count = min(TOK, last - base);
+        __syncthreads();           // everyone is done with the tokens staged before
+        if (MODE != 1) fetch(base);
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {
+            const int i = threadIdx.x + k * THREADS;
+            const int t = i / NPAD, n = i - t * NPAD;
+            sb[t][n] = to_float<T>(rb[k]);
+            sc[t][n] = to_float<T>(rc[k]);
+        }
+#pragma unroll
+        for (int k = 0; k < TOK * COLS / THREADS; ++k) {
+            const int i = threadIdx.x + k * THREADS;
+            sx[i / COLS][i % COLS] = to_float<T>(rx[k]);
+        }
+        if (threadIdx.x < TOK) {
+            const float dt = softplus(to_float<T>(rdt) + bias);
+            sdecay[threadIdx.x] = expf(-rate * dt);
+            sdt[threadIdx.x] = dt;
         }
         __syncthreads();
+        if (MODE == 1 && base + TOK < last) fetch(base + TOK);
         for (int t = 0; t < count; ++t) {
             const float decay = sdecay[t], x = sx[t][lane];
+            const float enters = sdt[t] * x;              // dt x: what B is multiplied with
             float sum = 0.f;
 #pragma unroll
             for (int i = 0; i < NR; ++i) {
                 const int n = warp + LANES * i;
-                s[i] = fmaf(decay, s[i], sb[t][n] * x);
+                s[i] = fmaf(decay, s[i], sb[t][n] * enters);
                 if (MODE != 1) sum = fmaf(s[i], sc[t][n], sum);
             }
             if (MODE != 1) partial[t][warp][lane] = sum;
