@@ -188,7 +188,8 @@ __global__ void gate_heads_kernel(const T* __restrict__ values, const T* __restr
     const int head = c / value_dim, e = c - head * value_dim;
     const float g = to_float<T>(gate[t * ld_gate + (per_head ? head : c)]);
     const float v = to_float<T>(values[(t * heads + head) * row_dim + e]);
-    out[i] = from_float<T>(v / (1.f + expf(-g)));
+    // (16-bit storage: the hardware's exponential and reciprocal, far inside its rounding)
+    out[i] = from_float<T>(sizeof(T) == 2 ? v * __frcp_rn(1.f + __expf(-g)) : v / (1.f + expf(-g)));
 }
 
 }  // namespace

@@ -30,6 +30,14 @@
 namespace {
 
 __device__ __forceinline__ float silu(float z) { return z / (1.f + expf(-z)); }
+// silu of a value that is stored in T next: for 16-bit storage the hardware's exponential and
+// reciprocal (a few units in the last place of 32 bits, far inside the storage's rounding) in
+// place of the exact ones, which are most of a streaming kernel's instructions
+template <typename T>
+__device__ __forceinline__ float silu_for(float z) {
+    if (sizeof(T) == 2) return z * __frcp_rn(1.f + __expf(-z));
+    return silu(z);
+}
 __device__ __forceinline__ float softplus(float z) { return z > 30.f ? z : log1pf(expf(z)); }
 
 // ------------------------------------------------------------------ convolution over time
@@ -68,19 +76,22 @@ channel_conv_kernel(const T* __restrict__ rows, int ld, const float* __restrict_
         }
         sum = fmaf(w[j], u, sum);
     }
-    if (activation == 1) sum = silu(sum);
+    if (activation == 1) sum = silu_for<T>(sum);
     out[(size_t)t * channels + c] = from_float<T>(sum);
 }
 
 // The same, 16 bytes of channels a thread (8 bfloat16 or 4 float), for channel counts, row
-// strides and addresses that allow it and up to WIDE_TAPS taps: a thread keeps its channels'
-// weights in registers over a run of WIDE_TOKENS tokens, and every tap of a token is one 16-byte
-// load.
-constexpr int WIDE_THREADS = 64;
-constexpr int WIDE_TOKENS = 8;
-constexpr int WIDE_TAPS = 8;
+// strides and addresses that allow it and up to 8 taps (WIDE_TAPS: 4 or 8, the code for the
+// taps that are there). A block of 256 threads takes WIDE_GROUPS runs of channels and WIDE_TOKENS
+// tokens: its weights come once, coalesced, through shared memory into registers; a thread takes
+// every fourth token of the block's, and every tap of a token is one 16-byte load, all taps asked
+// for before the first is used. (Eight tokens a thread, unrolled, ran no faster than one: the
+// code no longer fitted the instruction cache, and every warp runs it once.)
+constexpr int WIDE_GROUPS = 64;
+constexpr int WIDE_THREADS = 4 * WIDE_GROUPS;
+constexpr int WIDE_TOKENS = 16;
 
-template <typename T>
+template <typename T, int WIDE_TAPS>
 __global__ void __launch_bounds__(WIDE_THREADS)
 channel_conv_wide_kernel(const T* __restrict__ rows, int ld, const float* __restrict__ kernel,
                          const float* __restrict__ bias, const T* __restrict__ state,
@@ -88,8 +99,15 @@ channel_conv_wide_kernel(const T* __restrict__ rows, int ld, const float* __rest
                          const int* __restrict__ request_start, const int* __restrict__ history,
                          T* __restrict__ out, int tokens, int channels, int taps, int activation) {
     constexpr int V = 16 / sizeof(T);
+    // the block's weights come in one run of the stored [channels, taps] and are kept tap by tap
+    __shared__ __align__(16) float staged[WIDE_TAPS][WIDE_GROUPS * V];
     griddep_launch();
-    const int group = blockIdx.x * WIDE_THREADS + threadIdx.x;
+    const int block_first = blockIdx.x * WIDE_GROUPS * V;
+    const int block_channels = min(WIDE_GROUPS * V, channels - block_first);
+    for (int i = threadIdx.x; i < block_channels * taps; i += WIDE_THREADS)
+        staged[i % taps][i / taps] = kernel[(size_t)block_first * taps + i];
+    __syncthreads();
+    const int group = blockIdx.x * WIDE_GROUPS + (threadIdx.x % WIDE_GROUPS);
     if (group >= channels / V) return;
     const int c = group * V;
     float w[V][WIDE_TAPS], b[V];
@@ -97,42 +115,53 @@ channel_conv_wide_kernel(const T* __restrict__ rows, int ld, const float* __rest
     for (int v = 0; v < V; ++v) {
         b[v] = bias != nullptr ? bias[c + v] : 0.f;
 #pragma unroll
-        for (int j = 0; j < WIDE_TAPS; ++j) w[v][j] = j < taps ? kernel[(size_t)(c + v) * taps + j] : 0.f;
+        for (int j = 0; j < WIDE_TAPS; ++j)
+            w[v][j] = j < taps ? staged[j][(threadIdx.x % WIDE_GROUPS) * V + v] : 0.f;
     }
     griddep_wait();
-    // (unrolled, so that the loads of all the run's tokens are on their way together)
-#pragma unroll
-    for (int k = 0; k < WIDE_TOKENS; ++k) {
+#pragma unroll 1
+    for (int k = threadIdx.x / WIDE_GROUPS; k < WIDE_TOKENS; k += WIDE_THREADS / WIDE_GROUPS) {
         const int t = blockIdx.y * WIDE_TOKENS + k;
-        if (t >= tokens) continue;
+        if (t >= tokens) break;
         const int r = token_request[t];
         const int first = request_start[r];
         const int before = history[r];
         float sum[V];
 #pragma unroll
         for (int v = 0; v < V; ++v) sum[v] = b[v];
+        // all taps' rows are asked for before any is used (a tap without a row reads the step's
+        // first row and counts for nothing)
+        uint4 tap[WIDE_TAPS];
+        bool have[WIDE_TAPS];
 #pragma unroll
         for (int j = 0; j < WIDE_TAPS; ++j) {
+            have[j] = false;
             if (j >= taps) continue;
             const int source = t - (taps - 1 - j);
-            const T* from = nullptr;
+            const T* from = rows + c;
             if (source >= first) {
                 from = rows + (size_t)source * ld + c;
+                have[j] = true;
             } else if (state != nullptr) {
                 const int row = taps - 1 - (first - source);
-                if (row >= 0 && before - (first - source) >= 0)
+                if (row >= 0 && before - (first - source) >= 0) {
                     from = state + ((size_t)slots[r] * (taps - 1) + row) * channels + c;
+                    have[j] = true;
+                }
             }
-            if (from == nullptr) continue;
-            const uint4 packed = *reinterpret_cast<const uint4*>(from);
-            const T* u = reinterpret_cast<const T*>(&packed);
+            tap[j] = *reinterpret_cast<const uint4*>(from);
+        }
+#pragma unroll
+        for (int j = 0; j < WIDE_TAPS; ++j) {
+            if (j >= taps || !have[j]) continue;
+            const T* u = reinterpret_cast<const T*>(&tap[j]);
 #pragma unroll
             for (int v = 0; v < V; ++v) sum[v] = fmaf(w[v][j], to_float<T>(u[v]), sum[v]);
         }
         uint4 packed;
         T* y = reinterpret_cast<T*>(&packed);
 #pragma unroll
-        for (int v = 0; v < V; ++v) y[v] = from_float<T>(activation == 1 ? silu(sum[v]) : sum[v]);
+        for (int v = 0; v < V; ++v) y[v] = from_float<T>(activation == 1 ? silu_for<T>(sum[v]) : sum[v]);
         *reinterpret_cast<uint4*>(out + (size_t)t * channels + c) = packed;
     }
 }
@@ -187,7 +216,7 @@ channel_conv_single_kernel(const T* __restrict__ rows, int ld, const float* __re
         }
         if (write) slot[(size_t)(taps - 2) * channels] = mine;
     }
-    if (activation == 1) sum = silu(sum);
+    if (activation == 1) sum = silu_for<T>(sum);
     out[(size_t)r * channels + c] = from_float<T>(sum);
 }
 
@@ -441,12 +470,12 @@ gated_group_norm_block_kernel(const float* __restrict__ y, const T* __restrict__
     const T* z = gate + (size_t)t * ld + (size_t)part * size;
     float squares = 0.f;
     for (int c = threadIdx.x; c < size; c += NORM_THREADS) {
-        const float v = row[c] * silu(to_float<T>(z[c]));
+        const float v = row[c] * silu_for<T>(to_float<T>(z[c]));
         squares = fmaf(v, v, squares);
     }
     const float inverse = rsqrtf(block_sum(squares, scratch) / (float)size + eps);
     for (int c = threadIdx.x; c < size; c += NORM_THREADS) {
-        const float v = row[c] * silu(to_float<T>(z[c]));
+        const float v = row[c] * silu_for<T>(to_float<T>(z[c]));
         out[(size_t)t * inner + (size_t)part * size + c] =
             from_float<T>(v * inverse * weight[(size_t)part * size + c]);
     }
@@ -475,11 +504,11 @@ gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ gate,
 #pragma unroll
     for (int k = 0; k < KEPT; ++k) {
         const int c = lane + 32 * k;
-        kept[k] = c < size ? row[c] * silu(to_float<T>(z[c])) : 0.f;
+        kept[k] = c < size ? row[c] * silu_for<T>(to_float<T>(z[c])) : 0.f;
         squares = fmaf(kept[k], kept[k], squares);
     }
     for (int c = lane + 32 * KEPT; c < size; c += 32) {
-        const float v = row[c] * silu(to_float<T>(z[c]));
+        const float v = row[c] * silu_for<T>(to_float<T>(z[c]));
         squares = fmaf(v, v, squares);
     }
     const float inverse = rsqrtf(warp_sum(squares) / (float)size + eps);
@@ -491,7 +520,7 @@ gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ gate,
         if (c < size) to[c] = from_float<T>(kept[k] * inverse * w[c]);
     }
     for (int c = lane + 32 * KEPT; c < size; c += 32)
-        to[c] = from_float<T>(row[c] * silu(to_float<T>(z[c])) * inverse * w[c]);
+        to[c] = from_float<T>(row[c] * silu_for<T>(to_float<T>(z[c])) * inverse * w[c]);
 }
 
 }  // namespace
@@ -530,10 +559,11 @@ MLXONE_API int mlxone_channel_conv(const void* rows, int ld, const float* kernel
             constexpr int V = 16 / sizeof(T);                                                      \
             const bool wide = channels % V == 0 && ld % V == 0 && (uintptr_t)rows % 16 == 0 &&     \
                               (uintptr_t)out % 16 == 0 && (uintptr_t)state % 16 == 0 &&            \
-                              taps <= WIDE_TAPS && tokens <= 65535 * WIDE_TOKENS;                  \
+                              taps <= 8 && tokens <= 65535 * WIDE_TOKENS;                          \
             if (wide)                                                                              \
-                e = launch_kernel(channel_conv_wide_kernel<T>,                                     \
-                                  dim3(ceil_div_host(channels / V, WIDE_THREADS),                  \
+                e = launch_kernel(taps <= 4 ? channel_conv_wide_kernel<T, 4>                       \
+                                            : channel_conv_wide_kernel<T, 8>,                      \
+                                  dim3(ceil_div_host(channels / V, WIDE_GROUPS),                   \
                                        ceil_div_host(tokens, WIDE_TOKENS)),                        \
                                   dim3(WIDE_THREADS), 0, stream, true, (const T*)rows, ld, kernel, \
                                   bias, (const T*)state, slots, token_request, request_start,      \
