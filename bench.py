@@ -1296,8 +1296,7 @@ def tirudra_kernels(width, batch, peak):
                                               shared_down=alone[i][1], shared_scale=others[1])
             else:
                 gated = ops.linear_swiglu(x, gate_up[i])
-                ops.scale_expert_columns(gated, weights, ff)
-                ops.scale_expert_columns(gated[:, at:], others[1].view(-1, 1), shared)
+                ops.scale_expert_columns(gated, weights, ff, tail=others[1])
                 y = ops.linear(gated, down[i])
             ops.add_scaled_rows(y, x, others[0])
             return y

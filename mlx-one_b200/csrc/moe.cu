@@ -100,12 +100,17 @@ route_experts_kernel(const T* __restrict__ x, int ld, const float* __restrict__ 
 // go to weights[t, experts]. The outputs behind them hand the token on as it is: the sum of their
 // chosen weights goes to others[0][t]. With `shared_gate` the router has one more row behind its
 // outputs, and others[1][t] = sigmoid of that row's product with the token.
+// The logits are what a step of few tokens waits for: a warp a row of the router, sixteen warps a
+// token, four values a lane and load (where the addresses allow) with four sums of their own, so
+// that a row's loads are on their way together; the sums are added in a fixed order.
+constexpr int GENERAL_THREADS = 512;
+
 template <typename T>
-__global__ void __launch_bounds__(ROUTE_THREADS)
+__global__ void __launch_bounds__(GENERAL_THREADS)
 route_general_kernel(const T* __restrict__ x, int ld, const float* __restrict__ router,
                      const float* __restrict__ correction, float* __restrict__ weights,
                      float* __restrict__ others, int tokens, int hidden, int experts, int outputs,
-                     int top, int softmax, int normalize, int shared_gate) {
+                     int top, int softmax, int normalize, int shared_gate, int wide) {
     __shared__ float score[MAX_EXPERTS + 1];
     __shared__ float choice[MAX_EXPERTS];
     griddep_launch();
@@ -114,14 +119,37 @@ route_general_kernel(const T* __restrict__ x, int ld, const float* __restrict__ 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const T* row = x + (size_t)t * ld;
     const int rows = outputs + (shared_gate ? 1 : 0);
-    for (int e = warp; e < rows; e += ROUTE_THREADS / 32) {
+    for (int e = warp; e < rows; e += GENERAL_THREADS / 32) {
         const float* w = router + (size_t)e * hidden;
         float sum = 0.f;
-        for (int c = lane; c < hidden; c += 32) sum = fmaf(to_float<T>(row[c]), w[c], sum);
+        if (wide) {
+            float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+            for (int c = lane * 4; c < hidden; c += 128) {
+                const float4 weight = *reinterpret_cast<const float4*>(w + c);
+                float value[4];
+                if (sizeof(T) == 2) {
+                    const uint2 packed = *reinterpret_cast<const uint2*>(row + c);
+                    const T* four = reinterpret_cast<const T*>(&packed);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) value[k] = to_float<T>(four[k]);
+                } else {
+                    const float4 four = *reinterpret_cast<const float4*>(row + c);
+                    value[0] = four.x; value[1] = four.y; value[2] = four.z; value[3] = four.w;
+                }
+                part[0] = fmaf(value[0], weight.x, part[0]);
+                part[1] = fmaf(value[1], weight.y, part[1]);
+                part[2] = fmaf(value[2], weight.z, part[2]);
+                part[3] = fmaf(value[3], weight.w, part[3]);
+            }
+            sum = (part[0] + part[1]) + (part[2] + part[3]);
+        } else {
+            for (int c = lane; c < hidden; c += 32) sum = fmaf(to_float<T>(row[c]), w[c], sum);
+        }
         sum = warp_sum(sum);
         if (lane == 0) score[e] = sum;
     }
-    for (int e = threadIdx.x; e < experts; e += ROUTE_THREADS)
+    for (int e = threadIdx.x; e < experts; e += GENERAL_THREADS)
         weights[(size_t)t * experts + e] = 0.f;
     __syncthreads();
     if (threadIdx.x != 0) return;
@@ -173,18 +201,20 @@ __global__ void add_scaled_rows_kernel(T* __restrict__ out, const T* __restrict_
     out[i] = from_float<T>(fmaf(factors[t], to_float<T>(x[t * ld + c]), to_float<T>(out[i])));
 }
 
-// x[t, e * width + f] *= weights[t, e] for e < experts (columns beyond experts * width stay).
+// x[t, e * width + f] *= weights[t, e] for e < experts; the `tail_width` columns behind them (a
+// shared expert's) *= tail[t] (tail null: columns beyond experts * width stay).
 template <typename T>
 __global__ void scale_expert_columns_kernel(T* __restrict__ x, int ld, const float* __restrict__ weights,
-                                            int experts, int width, long long total) {
+                                            int experts, int width, long long total,
+                                            const float* __restrict__ tail, int tail_width) {
     griddep_launch();
     griddep_wait();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
-    const int across = experts * width;
+    const int across = experts * width + tail_width;
     const long long t = i / across;
     const int c = (int)(i - t * across);
-    const float w = weights[t * experts + c / width];
+    const float w = c < experts * width ? weights[t * experts + c / width] : tail[t];
     T* at = x + t * ld + c;
     *at = from_float<T>(to_float<T>(*at) * w);
 }
@@ -390,21 +420,36 @@ MLXONE_API int mlxone_route_experts(const void* x, int ld, const float* router, 
     return 0;
 }
 
-MLXONE_API int mlxone_scale_expert_columns(void* x, int ld, const float* weights, int tokens,
-                                           int experts, int width, int dtype, cudaStream_t stream) {
+static int scale_expert_columns(void* x, int ld, const float* weights, int tokens, int experts,
+                                int width, const float* tail, int tail_width, int dtype,
+                                cudaStream_t stream) {
     if (tokens == 0) return 0;
-    MLXONE_REQUIRE(tokens > 0 && experts > 0 && width > 0 && ld >= experts * width,
-                   "scale_expert_columns: bad sizes");
-    const long long total = (long long)tokens * experts * width;
+    if (tail == nullptr) tail_width = 0;
+    MLXONE_REQUIRE(tokens > 0 && experts > 0 && width > 0 && tail_width >= 0 &&
+                       ld >= experts * width + tail_width, "scale_expert_columns: bad sizes");
+    const long long total = (long long)tokens * (experts * width + tail_width);
     const int blocks = ceil_div_host(total, 256);
     if (dtype == MLXONE_BF16)
         launch_kernel(scale_expert_columns_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream,
-                      true, (__nv_bfloat16*)x, ld, weights, experts, width, total);
+                      true, (__nv_bfloat16*)x, ld, weights, experts, width, total, tail, tail_width);
     else
         launch_kernel(scale_expert_columns_kernel<float>, dim3(blocks), dim3(256), 0, stream, true,
-                      (float*)x, ld, weights, experts, width, total);
+                      (float*)x, ld, weights, experts, width, total, tail, tail_width);
     MLXONE_LAUNCH_CHECK("scale_expert_columns");
     return 0;
+}
+
+MLXONE_API int mlxone_scale_expert_columns(void* x, int ld, const float* weights, int tokens,
+                                           int experts, int width, int dtype, cudaStream_t stream) {
+    return scale_expert_columns(x, ld, weights, tokens, experts, width, nullptr, 0, dtype, stream);
+}
+
+// ... and the `tail_width` columns behind the experts' multiplied by tail[t]
+MLXONE_API int mlxone_scale_expert_columns_tail(void* x, int ld, const float* weights, int tokens,
+                                                int experts, int width, const float* tail,
+                                                int tail_width, int dtype, cudaStream_t stream) {
+    return scale_expert_columns(x, ld, weights, tokens, experts, width, tail, tail_width, dtype,
+                                stream);
 }
 
 MLXONE_API int mlxone_route_general(const void* x, int ld, const float* router,
@@ -418,14 +463,18 @@ MLXONE_API int mlxone_route_general(const void* x, int ld, const float* router,
                    "route_general: 1 to %d outputs of the router", MAX_EXPERTS);
     MLXONE_REQUIRE(top > 0 && top <= 64 && top <= outputs, "route_general: top %d of %d outputs", top,
                    outputs);
+    // four values a load where rows start on 16 bytes (the router's) and on 4 values (the tokens')
+    const size_t value = dtype == MLXONE_BF16 ? 2 : 4;
+    const int wide = hidden % 4 == 0 && ld % 4 == 0 && (uintptr_t)x % (4 * value) == 0 &&
+                     (uintptr_t)router % 16 == 0;
     if (dtype == MLXONE_BF16)
-        launch_kernel(route_general_kernel<__nv_bfloat16>, dim3(tokens), dim3(ROUTE_THREADS), 0,
+        launch_kernel(route_general_kernel<__nv_bfloat16>, dim3(tokens), dim3(GENERAL_THREADS), 0,
                       stream, true, (const __nv_bfloat16*)x, ld, router, correction, weights, others,
-                      tokens, hidden, experts, outputs, top, softmax, normalize, shared_gate);
+                      tokens, hidden, experts, outputs, top, softmax, normalize, shared_gate, wide);
     else
-        launch_kernel(route_general_kernel<float>, dim3(tokens), dim3(ROUTE_THREADS), 0, stream, true,
-                      (const float*)x, ld, router, correction, weights, others, tokens, hidden,
-                      experts, outputs, top, softmax, normalize, shared_gate);
+        launch_kernel(route_general_kernel<float>, dim3(tokens), dim3(GENERAL_THREADS), 0, stream,
+                      true, (const float*)x, ld, router, correction, weights, others, tokens, hidden,
+                      experts, outputs, top, softmax, normalize, shared_gate, wide);
     MLXONE_LAUNCH_CHECK("route_general");
     return 0;
 }

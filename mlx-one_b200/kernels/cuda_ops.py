@@ -749,10 +749,21 @@ class CudaOps:
                    _c_int(group_score), _c_int(_dtype_code(x.dtype)))
         return weights
 
-    def scale_expert_columns(self, gated, weights, width):
-        """In place: gated[t, e * width + f] *= weights[t, e]; columns beyond the experts' stay."""
+    def scale_expert_columns(self, gated, weights, width, tail=None):
+        """In place: gated[t, e * width + f] *= weights[t, e]; columns beyond the experts' stay,
+        or, with ``tail`` (float32 [tokens]), are multiplied by tail[t] (a shared expert's gate)."""
         self._need_rows(gated, gated.dtype, "gated")
         self._need(weights, torch.float32, "weights")
+        if tail is not None:
+            self._need(tail, torch.float32, "tail")
+            rest = gated.shape[1] - weights.shape[1] * width
+            if tail.numel() != gated.shape[0] or rest < 0:
+                raise KernelError("one factor per token for the columns behind the experts'")
+            self._call("mlxone_scale_expert_columns_tail", _c_void_p(_ptr(gated)),
+                       _c_int(gated.stride(0)), _c_void_p(_ptr(weights)), _c_int(gated.shape[0]),
+                       _c_int(weights.shape[1]), _c_int(width), _c_void_p(_ptr(tail)), _c_int(rest),
+                       _c_int(_dtype_code(gated.dtype)))
+            return
         self._call("mlxone_scale_expert_columns", _c_void_p(_ptr(gated)), _c_int(gated.stride(0)),
                    _c_void_p(_ptr(weights)), _c_int(gated.shape[0]), _c_int(weights.shape[1]),
                    _c_int(width), _c_int(_dtype_code(gated.dtype)))

@@ -209,10 +209,8 @@ class RoutedExperts(FeedForward):
                 gated = self.ops.linear_swiglu(x, self.gate_up)
             else:
                 gated = self.ops.linear_gated(x, self.gate_up, self.activation)
-            self.ops.scale_expert_columns(gated, weights, self.width)
-            if shared_scale is not None:
-                self.ops.scale_expert_columns(gated[:, self.experts * self.width:],
-                                              shared_scale.view(-1, 1), self.shared_width)
+            # (the shared expert's columns, behind the experts', times its gate in the same pass)
+            self.ops.scale_expert_columns(gated, weights, self.width, tail=shared_scale)
             out = self.ops.linear(gated, self.down)
         if self.identity:
             self.ops.add_scaled_rows(out, x, others[0])

@@ -182,10 +182,13 @@ class PlainOps:
                 weights[t, e] = float(row[e]) / total
         return weights
 
-    def scale_expert_columns(self, gated, weights, width):
+    def scale_expert_columns(self, gated, weights, width, tail=None):
         experts = weights.shape[1]
         scaled = gated[:, :experts * width].float().view(-1, experts, width) * weights[:, :, None]
         gated[:, :experts * width] = scaled.view(-1, experts * width).to(gated.dtype)
+        if tail is not None:
+            rest = gated[:, experts * width:].float() * tail[:, None]
+            gated[:, experts * width:] = rest.to(gated.dtype)
 
     def lightning_attention(self, projected, *, decay, norm_weight, eps, ctx, view, write, heads,
                             key_dim, value_dim):
